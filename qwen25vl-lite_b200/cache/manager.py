@@ -50,20 +50,29 @@ class CacheGroup:
     page_size: int
     stops: List[int]
     pool: PagePool
-    pages: Optional[torch.Tensor] = None   # [len(stops), 2, num_pages, kv_heads, page_size, head_dim]
+    # keys [len(stops), num_pages, kv_heads, page_size, head_dim] and values [..., value size]: two
+    # views of one tensor [len(stops), 2, ...] when the sizes are equal, else two tensors
+    k_pages: Optional[torch.Tensor] = None
+    v_pages: Optional[torch.Tensor] = None
 
     @property
     def window(self) -> Optional[int]:
         return self.need.window
 
     def first_needed_page(self, num_tokens: int) -> int:
-        """Logical page of the oldest key that the token at index ``num_tokens`` still sees."""
+        """Logical page of the oldest key behind the kept first tokens that the token at index
+        ``num_tokens`` still sees."""
         if self.window is None:
             return 0
         return max(0, num_tokens - self.window + 1) // self.page_size
 
+    @property
+    def kept_pages(self) -> int:
+        """Leading logical pages that a window never releases: they hold the kept first tokens."""
+        return -(-self.need.keep_first // self.page_size) if self.window is not None else 0
+
     def bytes_per_token(self, element_size: int) -> int:
-        return 2 * len(self.stops) * self.need.kv_heads * self.need.head_dim * element_size
+        return len(self.stops) * self.need.kv_heads * (self.need.head_dim + self.need.v_dim) * element_size
 
 
 @dataclass(eq=False)
@@ -119,9 +128,10 @@ class CacheManager:
             if s.cache_of not in self.location:
                 raise ValueError(f"stop {i} reads the cache of stop {s.cache_of}, which keeps none")
             owner = self.groups[self.location[s.cache_of][0]].need
-            if s.cache is None or (s.cache.kv_heads, s.cache.head_dim) != (owner.kv_heads, owner.head_dim):
+            if s.cache is None or (s.cache.kv_heads, s.cache.head_dim, s.cache.v_dim) != (owner.kv_heads, owner.head_dim, owner.v_dim):
                 raise ValueError(f"stop {i} cannot read the cache of stop {s.cache_of}: shapes differ")
-            if owner.window is not None and (s.cache.window is None or s.cache.window > owner.window):
+            if owner.window is not None and (s.cache.window is None or s.cache.window > owner.window
+                                             or s.cache.keep_first > owner.keep_first):
                 raise ValueError(f"stop {i} needs keys that stop {s.cache_of}'s window no longer keeps")
             self.location[i] = self.location[s.cache_of]
         self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
@@ -129,18 +139,23 @@ class CacheManager:
     # ---- device memory -----------------------------------------------------------------
     def allocate_device(self, device, dtype: torch.dtype) -> None:
         for g in self.groups:
-            g.pages = torch.zeros((len(g.stops), 2, self.num_pages, g.need.kv_heads, self.page_size, g.need.head_dim),
-                                  dtype=dtype, device=device)
+            shape = (len(g.stops), self.num_pages, g.need.kv_heads, self.page_size)
+            if g.need.v_dim == g.need.head_dim:
+                both = torch.zeros((shape[0], 2, *shape[1:], g.need.head_dim), dtype=dtype, device=device)
+                g.k_pages, g.v_pages = both[:, 0], both[:, 1]
+            else:
+                g.k_pages = torch.zeros((*shape, g.need.head_dim), dtype=dtype, device=device)
+                g.v_pages = torch.zeros((*shape, g.need.v_dim), dtype=dtype, device=device)
         for i, need in self.state_needs.items():
             self.states[i] = torch.zeros((self.max_requests, *need.shape), dtype=getattr(torch, need.dtype), device=device)
 
     def nbytes(self) -> int:
-        return sum(g.pages.numel() * g.pages.element_size() for g in self.groups if g.pages is not None)
+        return sum(t.numel() * t.element_size() for g in self.groups for t in (g.k_pages, g.v_pages) if t is not None)
 
     def stop_pages(self, stop: int) -> Tuple[CacheGroup, torch.Tensor, torch.Tensor]:
         gi, li = self.location[stop]
         g = self.groups[gi]
-        return g, g.pages[li, 0], g.pages[li, 1]
+        return g, g.k_pages[li], g.v_pages[li]
 
     # ---- requests ----------------------------------------------------------------------
     @property
@@ -197,7 +212,7 @@ class CacheManager:
                 continue
             table = req.tables[g.index]
             upto = min(g.first_needed_page(req.num_tokens), len(table))
-            for i in range(req.released[g.index], upto):
+            for i in range(max(req.released[g.index], g.kept_pages), upto):
                 if table[i] >= 0:
                     g.pool.free([table[i]])
                     table[i] = -1

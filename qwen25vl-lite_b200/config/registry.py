@@ -38,7 +38,10 @@ def known_architectures():
 
 
 def resolve_architecture(raw_config: Dict[str, Any]) -> Architecture:
+    """By ``architectures[0]``, or by ``architecture`` (one name) in files that have no list."""
     names = raw_config.get("architectures")
+    if not names and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]
     if not names:
         raise ValueError(
             "config.json has no 'architectures' entry; known architectures: " + ", ".join(known_architectures()))

@@ -27,11 +27,12 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer = an arrangement (``block``) of a mixer, a feed-forward and its norms."""
+    """One layer = an arrangement (``block``) of a mixer, a feed-forward (None: the layer has
+    none, for blocks that allow it) and its norms."""
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: Tuple[PartSpec, ...]
     prefix: str = ""
     # the position encoding this layer's mixer applies; None: the model's (``ModelSpec.position``)

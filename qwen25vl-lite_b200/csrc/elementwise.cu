@@ -1,4 +1,6 @@
-// Embedding gather, fused residual-add + RMSNorm, SiLU-mul.
+// Embedding gather (alone, or with a learned position vector and the model's norm), fused
+// residual-add + RMSNorm (plain, or in groups with an update that is normalised on its way in),
+// SiLU-mul, clamped gated linear unit.
 //
 // Formulas (reference: zhangjianbang-nb/qwen25vl-lite):
 //   embedding   x[n,:] = E[token[n],:]                          src/qwen25vl_lite/text.py:213
@@ -111,6 +113,161 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   }
 }
 
+// ---- normalisation in groups ------------------------------------------------------------------------
+// A row of `hidden` values is cut into `groups` equal consecutive parts and each part is divided by
+// its own root mean square: v / sqrt(mean(part^2) + eps).  groups == 1 is the plain RMS norm.  The
+// squares of a part are summed thread by thread, then lanes, then warps, in an order that depends on
+// the sizes alone.  `inv` (shared, `groups` floats) receives 1 / rms of every part.
+template <bool EXACT>
+__device__ __forceinline__ void group_inverse_rms(const float* row_cache, int hidden, int groups, float eps, float* inv,
+                                                  float* scratch) {
+  const int width = hidden / groups;
+  for (int g = 0; g < groups; ++g) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float v = row_cache[g * width + c];
+      ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, scratch);
+    if (threadIdx.x == 0) inv[g] = EXACT ? 1.0f / sqrtf(total / (float)width + eps) : rsqrtf(total / (float)width + eps);
+  }
+  __syncthreads();
+}
+
+#define NORM_MAX_GROUPS 64
+
+// x[n,:] = norm_in_groups(E[token[n],:] + P[position[n],:]) * w: a token embedding with a learned
+// vector per position added before the model's norm; the float32 residual stream starts here.
+template <typename T, bool EXACT>
+__global__ void embed_position_norm_kernel(const T* __restrict__ table, const T* __restrict__ pos_table,
+                                           const int* __restrict__ ids, const int* __restrict__ positions,
+                                           const float* __restrict__ w, float eps, float* __restrict__ x, int hidden,
+                                           int vocab, int max_positions, int groups) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float row_cache[];  // hidden floats + 32 scratch + groups
+  float* scratch = row_cache + hidden;
+  float* inv = scratch + 32;
+  const int row = blockIdx.x;
+  int id = ids[row], p = positions[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);                      // the host validates both; never read outside
+  p = p < 0 ? 0 : (p >= max_positions ? max_positions - 1 : p);
+  const T* e = table + (size_t)id * hidden;
+  const T* q = pos_table + (size_t)p * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_cache[c] = to_f32(e[c]) + to_f32(q[c]);
+  __syncthreads();
+  group_inverse_rms<EXACT>(row_cache, hidden, groups, eps, inv, scratch);
+  const int width = hidden / groups;
+  float* dst = x + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = row_cache[c] * inv[c / width] * w[c];
+}
+
+// x[row] += d, where d = delta[row] as it is (dw == nullptr) or norm_in_groups(delta[row]) * dw (a
+// sublayer that is normalised after as well as before); then out[r] = norm_in_groups(x[row]) * w.
+// rows as in add_rmsnorm_kernel: with rows the sum is formed for those rows only and x is left alone.
+// out == nullptr: only the addition.
+template <typename T, bool EXACT>
+__global__ void add_norm_groups_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ dw,
+                                       float d_eps, int d_groups, const float* __restrict__ w, float eps, int groups,
+                                       T* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float row_cache[];  // 2 * hidden floats + 32 scratch + groups
+  float* d_cache = row_cache + hidden;
+  float* scratch = d_cache + hidden;
+  float* inv = scratch + 32;
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* xr = x + (size_t)row * hidden;
+  if (delta) {
+    const T* dr = delta + (size_t)row * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) d_cache[c] = to_f32(dr[c]);
+    __syncthreads();
+    if (dw) {
+      group_inverse_rms<EXACT>(d_cache, hidden, d_groups, d_eps, inv, scratch);
+      const int dwidth = hidden / d_groups;
+      for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = xr[c] + d_cache[c] * inv[c / dwidth] * dw[c];
+        row_cache[c] = v;
+        if (!rows) xr[c] = v;
+      }
+    } else {
+      for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = xr[c] + d_cache[c];
+        row_cache[c] = v;
+        if (!rows) xr[c] = v;
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_cache[c] = xr[c];
+  }
+  if (!out) return;
+  __syncthreads();
+  group_inverse_rms<EXACT>(row_cache, hidden, groups, eps, inv, scratch);
+  const int width = hidden / groups;
+  T* o = out + (size_t)r * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>(row_cache[c] * inv[c / width] * w[c]);
+}
+
+// Gated linear unit with clamped branches: gu is [n, 2*inter], gate in the first half of a row, up
+// in the second; g = min(g, limit), u = clamp(u, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1).
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter, float limit, float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)n * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / inter, c = i % inter;
+    const float g = fminf(to_f32(gu[row * 2 * inter + c]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[row * 2 * inter + inter + c]), -limit), limit);
+    out[i] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+  }
+}
+
+template <typename T, bool EXACT>
+static int embed_position_norm(const void* table, const void* pos_table, const int* ids, const int* positions, const float* w,
+                               float eps, float* x, int n, int hidden, int vocab, int max_positions, int groups, void* stream) {
+  if (n <= 0) return 0;
+  if (groups <= 0 || groups > NORM_MAX_GROUPS || hidden % groups) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)(hidden + 32 + NORM_MAX_GROUPS) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(embed_position_norm_kernel<T, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(embed_position_norm_kernel<T, EXACT>, dim3(n), dim3(hidden >= 1024 ? 256 : 128), smem, (cudaStream_t)stream,
+         (const T*)table, (const T*)pos_table, ids, positions, w, eps, x, hidden, vocab, max_positions, groups);
+  return launch_status();
+}
+
+template <typename T, bool EXACT>
+static int add_norm_groups(float* x, const void* delta, const float* dw, float d_eps, int d_groups, const float* w, float eps,
+                           int groups, void* out, const int* rows, int n_out, int hidden, void* stream) {
+  if (n_out <= 0) return 0;
+  if (groups <= 0 || groups > NORM_MAX_GROUPS || hidden % groups) return (int)cudaErrorInvalidValue;
+  if (dw && (d_groups <= 0 || d_groups > NORM_MAX_GROUPS || hidden % d_groups)) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)(2 * hidden + 32 + NORM_MAX_GROUPS) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(add_norm_groups_kernel<T, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(add_norm_groups_kernel<T, EXACT>, dim3(n_out), dim3(hidden >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, x,
+         (const T*)delta, dw, d_eps, d_groups, w, eps, groups, (T*)out, rows, hidden);
+  return launch_status();
+}
+
+template <typename T>
+static int glu_clamped(const void* gu, void* out, int n, int inter, float limit, float alpha, void* stream) {
+  if (n <= 0) return 0;
+  const size_t total = (size_t)n * inter;
+  size_t blocks = (total + 255) / 256;
+  const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
+  if (blocks > most) blocks = most;
+  launch(glu_clamped_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha);
+  return launch_status();
+}
+
 template <typename T>
 static int embed_gather(const void* table, const int* ids, float* x, int n, int hidden, int vocab, void* stream) {
   if (n <= 0) return 0;
@@ -153,6 +310,13 @@ Q25_EXPORT int q25_add_rmsnorm_f32(float* x, const void* d, const float* w, floa
 Q25_EXPORT int q25_add_rmsnorm_bf16(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<bf16, false>(x, d, w, eps, o, rows, n, h, s); }
 Q25_EXPORT int q25_silu_mul_f32(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<float>(gu, o, n, inter, paired, s); }
 Q25_EXPORT int q25_silu_mul_bf16(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<bf16>(gu, o, n, inter, paired, s); }
+
+Q25_EXPORT int q25_embed_position_norm_f32(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, void* s) { return embed_position_norm<float, true>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, s); }
+Q25_EXPORT int q25_embed_position_norm_bf16(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, void* s) { return embed_position_norm<bf16, false>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, s); }
+Q25_EXPORT int q25_add_norm_groups_f32(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<float, true>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
+Q25_EXPORT int q25_add_norm_groups_bf16(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<bf16, false>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
+Q25_EXPORT int q25_glu_clamped_f32(const void* gu, void* o, int n, int inter, float limit, float alpha, void* s) { return glu_clamped<float>(gu, o, n, inter, limit, alpha, s); }
+Q25_EXPORT int q25_glu_clamped_bf16(const void* gu, void* o, int n, int inter, float limit, float alpha, void* s) { return glu_clamped<bf16>(gu, o, n, inter, limit, alpha, s); }
 
 // Streaming multiprocessors of the current device (0 if it cannot be read).
 Q25_EXPORT int q25_sm_count(void) { return device_sm_count(); }

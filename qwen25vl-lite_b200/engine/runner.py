@@ -190,7 +190,7 @@ class ModelRunner:
         # part of the model says its forward can be captured (``graph_safe``: a fixed sequence of this
         # engine's kernels, no host-side loop over the batch, no library operator that synchronises).
         blocks = getattr(model, "blocks", [])
-        parts = [p for b in blocks for p in (b.mixer, b.feed_forward, *b.norms)]
+        parts = [p for b in blocks for p in (b.mixer, b.feed_forward, *b.norms) if p is not None]
         parts += [getattr(model, name, None) for name in ("embedding", "final_norm", "head")]
         parts += model.position_encodings() if hasattr(model, "position_encodings") else [model.position]
         self.cuda_graphs = bool(cuda_graphs and self.device.type == "cuda" and blocks
@@ -517,6 +517,9 @@ class ModelRunner:
                     gt[i, :len(table)] = table
                     gt[i, len(table):] = 0
 
+        limit = getattr(self.position, "limit", None)
+        if limit is not None and N and int(pos.max()) >= limit:
+            raise ValueError(f"a token sits at position {int(pos.max())}, the model places positions 0 to {limit - 1}")
         return lambda tokens=None, device_ids=None: self._run_packed(
             tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s, cu_s, qs_s, sl_s,
             rows_s, g_slot_s, g_tab_s, plan_s, last_position, pad_cache, device_ids)

@@ -72,7 +72,7 @@ def replay(lines: Iterable[str], runner: ModelRunner, out_dir: Optional[str], re
         reply.flush()
 
 
-def make_runner(model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, max_requests: int = 8,
+def make_runner(model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, max_requests: int = 4,
                 device: str = "cuda:0") -> ModelRunner:
     """A runner whose pools hold ``max_tokens`` tokens (a multiple of 64) per cache group."""
     if max_tokens <= 0 or max_tokens % 64:
@@ -93,7 +93,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a cache page (divides 64)")
-    ap.add_argument("--max-requests", type=int, default=8, help="per-request state slots")
+    ap.add_argument("--max-requests", type=int, default=4, help="per-request state slots (live requests)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     runner = make_runner(args.model, args.dtype, args.max_tokens, args.page_size, args.max_requests, args.device)

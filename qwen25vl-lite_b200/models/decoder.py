@@ -45,11 +45,12 @@ class DecoderModel:
                 raise ValueError(f"unknown block kind {layer.block!r}; known: {sorted(parts.BLOCKS)}")
             mixer = parts.build_part(parts.MIXERS, layer.mixer, "mixer",
                                      position=self._position_for(layer.position or spec.position))
-            ffn = parts.build_part(parts.FEED_FORWARDS, layer.feed_forward, "feed-forward")
+            ffn = None if layer.feed_forward is None else parts.build_part(parts.FEED_FORWARDS, layer.feed_forward, "feed-forward")
             norms = [parts.build_part(parts.NORMS, n, "norm") for n in layer.norms]
             self.blocks.append(parts.BLOCKS[layer.block](mixer, ffn, norms))
             self._named_parts.append((layer.prefix + layer.mixer.prefix, mixer))
-            self._named_parts.append((layer.prefix + layer.feed_forward.prefix, ffn))
+            if ffn is not None:
+                self._named_parts.append((layer.prefix + layer.feed_forward.prefix, ffn))
             for nspec, n in zip(layer.norms, norms):
                 self._named_parts.append((layer.prefix + nspec.prefix, n))
         self.final_norm = parts.build_part(parts.NORMS, spec.final_norm, "norm")

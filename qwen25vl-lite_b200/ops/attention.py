@@ -253,3 +253,34 @@ def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window
             kernels.attention_prefill(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles64,
                                       nq, nkv, head_dim, kv.page_size, window, scale)
     return out
+
+
+# ---- attention with a distance bias, a window beside kept first tokens, values of their own size ---------
+
+
+def plan_biased(host, group: int, window: int, keep_first: int) -> Dict[str, np.ndarray]:
+    """Work lists of the kernels of ``parts.attention.BiasedWindowAttention`` for a step: the entries
+    that bring one token (``decode_items``) and (entry, row tile) pairs of the runs, a tile being
+    64 consecutive (token, head of the group) rows; the tiles that walk the most keys go first."""
+    q_lens, starts = host.q_lens, host.starts
+    singles = [i for i, n in enumerate(q_lens) if n == 1]
+    runs = [i for i, n in enumerate(q_lens) if n > 1]
+
+    def keys(i, t):                     # keys the tile's last token sees
+        last = starts[i] + min((t * 64 + 63) // group, q_lens[i] - 1)
+        return last + 1 if not window or last < window + keep_first else window + keep_first
+
+    pairs = [(i, t) for i in runs for t in range(-(-q_lens[i] * group // 64))]
+    pairs.sort(key=lambda it: -keys(*it))
+    return {"decode_items": np.asarray(singles, dtype=np.int32), "tiles64": np.asarray(pairs, dtype=np.int32).reshape(-1)}
+
+
+def attend_biased(ctx, plan, qkv, kv, nq: int, nkv: int, dk: int, dv: int, window, keep_first: int, scale: float,
+                  r1, r2) -> torch.Tensor:
+    """qkv: [N, nq*dk + nkv*dk + nkv*dv] as projected, this step's keys and values already in the
+    pages.  Returns [N, nq * dv]."""
+    out = torch.empty((qkv.shape[0], nq * dv), dtype=qkv.dtype, device=qkv.device)
+    kernels.biased_attention_generic(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.token_seq, ctx.cu_q,
+                                     ctx.q_start_pos, nq, nkv, dk, dv, kv.page_size, int(window or 0), int(keep_first or 0),
+                                     scale, r1, r2)
+    return out

@@ -26,6 +26,17 @@ _SIGNATURES = {
     "q25_silu_mul": [_P, _P, _I, _I, _I, _P],
     "q25_rope_store": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "q25_embed_position_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P],
+    "q25_add_norm_groups": [_P, _P, _P, _F, _I, _P, _F, _I, _P, _P, _I, _I, _P],
+    "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _P],
+    "q25_rglru_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_rglru_scan": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
+    "q25_kv_store_mix": [_P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "q25_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "q25_moe_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "q25_moe_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
 _UNTYPED = {
     "q25_attention_decode_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -58,9 +69,18 @@ def load_library(name: str = "core") -> ctypes.CDLL:
     return lib
 
 
-# symbols of the tensor-core kernels, which only the bfloat16 path loads (and so compiles)
-_BF16_SYMBOLS = ("q25_attention_decode", "q25_attention_prefill", "q25_gemm_chain", "q25_gemm_tcgen05",
-                 "q25_rope_angles")
+# which library holds a symbol, by the symbol's beginning (everything else is in "core"); a
+# library is compiled and loaded when one of its kernels is first asked for
+_SYMBOL_LIBRARY = (("q25_gemm_chain", "chain"), ("q25_attention_decode", "bf16"), ("q25_attention_prefill", "bf16"),
+                   ("q25_gemm_tcgen05", "bf16"), ("q25_rope_angles", "bf16"), ("q25_rglru", "recurrent"),
+                   ("q25_biased_attention", "biased"), ("q25_kv_store_mix", "biased"), ("q25_moe", "routed"))
+
+
+def _library_of(symbol: str) -> str:
+    for prefix, library in _SYMBOL_LIBRARY:
+        if symbol.startswith(prefix):
+            return library
+    return "core"
 
 
 def _fn(symbol: str, argtypes, library: Optional[str] = None):
@@ -68,7 +88,7 @@ def _fn(symbol: str, argtypes, library: Optional[str] = None):
         chain_flush()                       # products that wait in the chain come before this kernel
     f = _fns.get(symbol)
     if f is None:
-        lib = load_library(library or ("bf16" if symbol.startswith(_BF16_SYMBOLS) else "core"))
+        lib = load_library(library or _library_of(symbol))
         try:
             f = getattr(lib, symbol)
         except AttributeError as exc:
@@ -602,3 +622,177 @@ def apply_penalties(logits: torch.Tensor, ids: torch.Tensor, counts: torch.Tenso
     _check(_fn("q25_apply_penalties", _UNTYPED["q25_apply_penalties"])(
         logits.data_ptr(), logits.stride(0), rows, vocab, ids.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
         repetition.data_ptr(), presence.data_ptr(), frequency.data_ptr(), _stream()), "apply_penalties")
+
+
+# ---- a token embedding with learned positions; norms in groups; the clamped gated unit -----------
+
+
+def embed_position_norm(table: torch.Tensor, pos_table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                        weight: torch.Tensor, eps: float, groups: int, x_out: torch.Tensor) -> None:
+    """x_out[n, :] (float32) = norm_in_groups(table[ids[n]] + pos_table[positions[n]]) * weight."""
+    n, hidden = x_out.shape
+    _dev(ids, torch.int32, "embed_position_norm ids"); _dev(positions, torch.int32, "embed_position_norm positions")
+    _dev(x_out, torch.float32, "embed_position_norm out"); _dev(weight, torch.float32, "embed_position_norm weight")
+    if pos_table.dtype != table.dtype or hidden % groups:
+        raise KernelError("embed_position_norm: the two tables share a dtype and the groups divide the width")
+    _check(_typed("q25_embed_position_norm", table.dtype)(
+        table.data_ptr(), pos_table.data_ptr(), ids.data_ptr(), positions.data_ptr(), weight.data_ptr(), float(eps),
+        x_out.data_ptr(), n, hidden, table.shape[0], pos_table.shape[0], int(groups), _stream()), "embed_position_norm")
+
+
+def add_norm_groups(x: torch.Tensor, delta: Optional[torch.Tensor], delta_weight: Optional[torch.Tensor], delta_eps: float,
+                    delta_groups: int, weight: Optional[torch.Tensor], eps: float, groups: int,
+                    out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None, dtype: Optional[torch.dtype] = None) -> None:
+    """x += d with d = delta, or norm_in_groups(delta) * delta_weight when a weight is given; then
+    out = norm_in_groups(x) * weight (out None: only the addition).  ``rows`` as for ``add_rmsnorm``."""
+    hidden = x.shape[-1]
+    dtype = out.dtype if out is not None else (delta.dtype if delta is not None else dtype)
+    n_out = out.shape[0] if out is not None else (rows.shape[0] if rows is not None else x.shape[0])
+    _dev(x, torch.float32, "add_norm_groups x")
+    if delta is not None:
+        _dev(delta, dtype, "add_norm_groups delta")
+    for t in (delta_weight, weight):
+        if t is not None:
+            _dev(t, torch.float32, "add_norm_groups weight")
+    if rows is not None:
+        _dev(rows, torch.int32, "add_norm_groups rows")
+    _check(_typed("q25_add_norm_groups", dtype)(
+        x.data_ptr(), _ptr(delta), _ptr(delta_weight), float(delta_eps), int(delta_groups), _ptr(weight), float(eps), int(groups),
+        _ptr(out), _ptr(rows), n_out, hidden, _stream()), "add_norm_groups")
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit);
+    ``gate_up`` rows hold the gate features, then the up features."""
+    n, inter = out.shape
+    _dev(gate_up, out.dtype, "glu_clamped input")
+    _check(_typed("q25_glu_clamped", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, float(limit), float(alpha), _stream()),
+           "glu_clamped")
+
+
+# ---- the gated linear recurrence -------------------------------------------------------------------
+
+
+def rglru_conv(yx: torch.Tensor, x_off: int, conv_w: torch.Tensor, conv_b: torch.Tensor, state: torch.Tensor,
+               token_seq: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor, u_out: torch.Tensor) -> None:
+    """u_out[n, c] (float32) = causal convolution over the request's inputs ``yx[:, x_off + c]``, the
+    ``taps - 1`` inputs before the step's first token taken from ``state`` [slots, taps, width]."""
+    n, width = u_out.shape
+    taps = conv_w.shape[1]
+    _dev(u_out, torch.float32, "rglru_conv out"); _dev(state, torch.float32, "rglru_conv state")
+    _dev(conv_w, torch.float32, "rglru_conv weight"); _dev(conv_b, torch.float32, "rglru_conv bias")
+    if tuple(state.shape[1:]) != (taps, width) or yx.stride(1) != 1:
+        raise KernelError(f"rglru_conv: state must be [slots, {taps}, {width}]")
+    _check(_typed("q25_rglru_conv", yx.dtype)(yx.data_ptr(), yx.stride(0), int(x_off), conv_w.data_ptr(), conv_b.data_ptr(),
+                                              state.data_ptr(), token_seq.data_ptr(), cu_q.data_ptr(), slot_ids.data_ptr(),
+                                              u_out.data_ptr(), n, width, taps, _stream()), "rglru_conv")
+
+
+def rglru_gates(u: torch.Tensor, ra: torch.Tensor, ra_b: torch.Tensor, ri: torch.Tensor, ri_b: torch.Tensor, lam: torch.Tensor,
+                gain: float, a_out: torch.Tensor, bx_out: torch.Tensor) -> None:
+    """The recurrence's decay a = exp(-gain * sigmoid(Ra u + b) * softplus(lam)) and input term
+    sqrt(1 - a^2) * sigmoid(Ri u + b) * u, per block of channels, all float32."""
+    n, width = u.shape
+    blocks = ra.shape[0]
+    for t in (u, ra, ra_b, ri, ri_b, lam, a_out, bx_out):
+        _dev(t, torch.float32, "rglru_gates")
+    _check(_fn("q25_rglru_gates", [_P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P])(
+        u.data_ptr(), ra.data_ptr(), ra_b.data_ptr(), ri.data_ptr(), ri_b.data_ptr(), lam.data_ptr(), float(gain),
+        a_out.data_ptr(), bx_out.data_ptr(), n, width, blocks, _stream()), "rglru_gates")
+
+
+def rglru_scan(a: torch.Tensor, bx: torch.Tensor, yx: torch.Tensor, y_off: int, x_off: int, state: torch.Tensor,
+               cu_q: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor, n_seqs: int) -> None:
+    """S = a S + bx over every entry's tokens from the request's state (row 0 of ``state``), out = S *
+    gelu_tanh(yx[:, y_off + c]); the state (S and the last taps - 1 inputs) moves on."""
+    width = out.shape[1]
+    taps = state.shape[1]
+    _dev(out, yx.dtype, "rglru_scan out")
+    _check(_typed("q25_rglru_scan", yx.dtype)(a.data_ptr(), bx.data_ptr(), yx.data_ptr(), yx.stride(0), int(y_off), int(x_off),
+                                              state.data_ptr(), cu_q.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), int(n_seqs),
+                                              width, taps, _stream()), "rglru_scan")
+
+
+# ---- attention with a distance bias, kept first tokens and values of their own size ---------------------
+
+
+def kv_store_mix(qkv: torch.Tensor, v_other: Optional[torch.Tensor], mix: float, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                 kv_slot: torch.Tensor, nq: int, nkv: int, dk: int, dv: int, page_size: int) -> None:
+    """Writes the step's keys and values into the pages at ``kv_slot``; with ``v_other`` (rows of
+    nkv * dv values of the same tokens) the values become (1 - mix) v + mix v_other first."""
+    if v_other is not None and (v_other.dtype != qkv.dtype or v_other.stride(1) != 1 or v_other.shape != (qkv.shape[0], nkv * dv)):
+        raise KernelError("kv_store_mix: the other values must be rows of nkv * dv channels of the same tokens")
+    _check(_typed("q25_kv_store_mix", qkv.dtype)(
+        qkv.data_ptr(), qkv.stride(0), _ptr(v_other), 0 if v_other is None else v_other.stride(0), float(mix), k_pages.data_ptr(),
+        v_pages.data_ptr(), kv_slot.data_ptr(), qkv.shape[0], nq, nkv, dk, dv, page_size, _stream()), "kv_store_mix")
+
+
+def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                             block_table: torch.Tensor, token_seq: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor,
+                             nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
+                             r1: Optional[torch.Tensor], r2: Optional[torch.Tensor]) -> None:
+    if dv > 256:
+        raise KernelError(f"attention: value size {dv} is beyond 256")
+    _check(_typed("q25_biased_attention_generic", qkv.dtype)(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], token_seq.data_ptr(), cu_q.data_ptr(), q_start_pos.data_ptr(), qkv.shape[0], nq, nkv, dk, dv,
+        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _stream()), "biased_attention_generic")
+
+
+# ---- the routed feed-forward ------------------------------------------------------------------------
+
+
+def moe_max_rows(n_pairs: int, experts: int, tile: int) -> int:
+    """Rows the sorted (token, expert) pairs can take: every expert's rows fill whole tiles."""
+    return (-(-n_pairs // tile) + experts) * tile
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, shared_gate: Optional[torch.Tensor], top: int, topk_idx: torch.Tensor,
+              topk_w: torch.Tensor, sg: Optional[torch.Tensor], counts: torch.Tensor) -> None:
+    """Router logits in float32, the ``top`` largest (weights sigmoid(logit)), the shared expert's
+    gate sigmoid(shared_gate . h), and how many tokens chose each expert (added into ``counts``)."""
+    n, hidden = h.shape
+    _dev(router, torch.float32, "moe_route router"); _dev(topk_idx, torch.int32, "moe_route idx")
+    _dev(topk_w, torch.float32, "moe_route weights"); _dev(counts, torch.int32, "moe_route counts")
+    _check(_typed("q25_moe_route", h.dtype)(h.data_ptr(), router.data_ptr(), _ptr(shared_gate), topk_idx.data_ptr(),
+                                            topk_w.data_ptr(), _ptr(sg), counts.data_ptr(), n, hidden, router.shape[0], int(top),
+                                            _stream()), "moe_route")
+
+
+def moe_sort(topk_idx: torch.Tensor, counts: torch.Tensor, cursor: torch.Tensor, plan: torch.Tensor, row_pair: torch.Tensor,
+             pair_row: torch.Tensor, experts: int, tile: int) -> None:
+    """Lays the pairs out by expert: ``plan`` = [tiles, first row of each expert ..., end, expert of each
+    tile ...], ``row_pair`` the pair of every row (-1: empty), ``pair_row`` the row of every pair."""
+    n_pairs = topk_idx.numel()
+    if plan.numel() < 2 + experts + moe_max_rows(n_pairs, experts, tile) // tile or row_pair.numel() < moe_max_rows(n_pairs, experts, tile):
+        raise KernelError("moe_sort: the plan or the row list is too short")
+    _check(_fn("q25_moe_sort", [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P])(
+        topk_idx.data_ptr(), counts.data_ptr(), cursor.data_ptr(), plan.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(),
+        n_pairs, experts, tile, _stream()), "moe_sort")
+    count_replayed(1)                          # two kernels in one call
+
+
+def moe_gate_up(h: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, act: torch.Tensor, plan: torch.Tensor,
+                row_pair: torch.Tensor, topk_w: torch.Tensor, top: int, limit: float, alpha: float, tile: int) -> None:
+    experts, ff, hidden = w_gate.shape
+    _dev(w_gate, h.dtype, "moe_gate_up gate"); _dev(w_up, h.dtype, "moe_gate_up up"); _dev(act, h.dtype, "moe_gate_up act")
+    _check(_typed("q25_moe_gate_up", h.dtype)(h.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), act.data_ptr(), plan.data_ptr(),
+                                              row_pair.data_ptr(), topk_w.data_ptr(), topk_w.numel(), experts, int(top), ff, hidden,
+                                              float(limit), float(alpha), int(tile), _stream()), "moe_gate_up")
+
+
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor, plan: torch.Tensor, row_pair: torch.Tensor, n_pairs: int,
+             top: int, tile: int) -> None:
+    experts, hidden, ff = w_down.shape
+    _dev(w_down, act.dtype, "moe_down weight"); _dev(y, torch.float32, "moe_down out")
+    _check(_typed("q25_moe_down", act.dtype)(act.data_ptr(), w_down.data_ptr(), y.data_ptr(), plan.data_ptr(), row_pair.data_ptr(),
+                                             int(n_pairs), experts, int(top), hidden, ff, int(tile), _stream()), "moe_down")
+
+
+def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, sg: Optional[torch.Tensor], shared: Optional[torch.Tensor],
+                out: torch.Tensor, top: int) -> None:
+    n, hidden = out.shape
+    if shared is not None:
+        _dev(shared, out.dtype, "moe_combine shared")
+    _check(_typed("q25_moe_combine", out.dtype)(y.data_ptr(), pair_row.data_ptr(), _ptr(sg), _ptr(shared), out.data_ptr(), n, hidden,
+                                                int(top), _stream()), "moe_combine")

@@ -34,11 +34,19 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class KVCacheNeed:
-    """Pages of keys and values: all keys (window None) or the last ``window`` of them."""
+    """Pages of keys and values: all keys (window None) or the last ``window`` of them, beside
+    which the first ``keep_first`` tokens of the request stay readable for good.  ``value_dim``:
+    the size of a value when it is not the key's."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+    keep_first: int = 0
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -47,6 +55,15 @@ class StateNeed:
 
     shape: Tuple[int, ...]
     dtype: str = "float32"
+
+
+class PendingUpdate:
+    """An update of the residual stream that has not been added yet and is to be normalised on its
+    way in: ``x += norm(value)``.  A block whose sublayers are normalised after as well as before
+    returns one as its pending update, and the norm kernel that adds it does both."""
+
+    def __init__(self, value: torch.Tensor, norm: "Norm"):
+        self.value, self.norm = value, norm
 
 
 class Part:
@@ -122,6 +139,7 @@ class PositionEncoding(Part):
 
     axes = 1
     default_is_linear = False
+    limit = None                    # positions run from 0 to limit - 1 (None: no end); the step function refuses others
 
     def default_positions(self, start: int, count: int, offset: int):
         raise NotImplementedError

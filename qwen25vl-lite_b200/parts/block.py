@@ -9,7 +9,7 @@ run yet, to be computed inside its first product."""
 
 from __future__ import annotations
 
-from .base import Block, register_block
+from .base import Block, PendingUpdate, register_block
 
 
 @register_block("prenorm_residual")
@@ -25,3 +25,20 @@ class PreNormResidualBlock(Block):
         if ffn.accepts_residual:
             return ffn.forward(ctx, h, residual=x)
         return ffn.forward(ctx, h)
+
+
+@register_block("sandwich_residual")
+class SandwichResidualBlock(Block):
+    """Every sublayer is normalised before and after: ``x += norm1b(mixer(norm1(x)))``, then
+    ``x += norm2b(ffn(norm2(x)))``; the norms come in that order (norm1, norm1b, norm2, norm2b).  A
+    layer without a feed-forward has the mixer's two norms only.  The norm after a sublayer runs
+    inside the kernel that adds the sublayer's result and normalises for the next one: the block
+    hands its last result on as a ``PendingUpdate``."""
+
+    def forward(self, ctx, x, pending, stop):
+        h = self.norms[0].forward(ctx, x, pending)
+        mixed = PendingUpdate(self.mixer.forward(ctx, h, stop), self.norms[1])
+        if self.feed_forward is None:
+            return mixed
+        h = self.norms[2].forward(ctx, x, mixed)
+        return PendingUpdate(self.feed_forward.forward(ctx, h), self.norms[3])

@@ -35,21 +35,61 @@ class TokenEmbedding(Part):
         return x
 
 
+@register_embedding("learned_position_embedding")
+class LearnedPositionEmbedding(Part):
+    """``x = norm(E[token] + P[position])``: a token table, a learned vector per position (added as it
+    is), and a norm (in ``norm_groups`` groups) whose result starts the residual stream.  One kernel.
+    The tensors' names in a checkpoint are parameters."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
+    def __init__(self, vocab_size: int, hidden_size: int, max_positions: int, norm_eps: float, norm_groups: int = 1,
+                 names=("weight", "positions", "norm")):
+        self.vocab_size, self.hidden_size, self.max_positions = int(vocab_size), int(hidden_size), int(max_positions)
+        self.norm_eps, self.norm_groups = float(norm_eps), int(norm_groups)
+        if self.norm_groups < 1 or self.hidden_size % self.norm_groups:
+            raise ValueError(f"a norm over {hidden_size} channels cannot be cut into {norm_groups} equal groups")
+        self.token_name, self.position_name, self.norm_name = names
+        self.weight = self.positions = self.norm_weight = None
+
+    def tensor_specs(self):
+        return (TensorSpec(self.token_name, (self.vocab_size, self.hidden_size)),
+                TensorSpec(self.position_name, (self.max_positions, self.hidden_size)),
+                TensorSpec(self.norm_name, (self.hidden_size,), init="norm"))
+
+    def load(self, tensors, device, dtype):
+        self.weight = tensors[self.token_name].to(device=device, dtype=dtype).contiguous()
+        self.positions = tensors[self.position_name].to(device=device, dtype=dtype).contiguous()
+        self.norm_weight = tensors[self.norm_name].to(device=device, dtype=torch.float32).contiguous()
+
+    def exports(self):
+        return {self.token_name: self.weight}
+
+    def forward(self, ctx):
+        x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
+        kernels.embed_position_norm(self.weight, self.positions, ctx.token_ids, ctx.positions[0], self.norm_weight,
+                                    self.norm_eps, self.norm_groups, x)
+        return x
+
+
 @register_head("linear_head")
 class LinearHead(Part):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
     accepts_deferred_norm = True     # its product is a ``Linear``, which normalises inside the kernel when it can
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool, tied_to: str = "embed_tokens.weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool, tied_to: str = "embed_tokens.weight",
+                 name: str = "weight"):
         """``tied``: without a weight of its own in the checkpoint the head reads the tensor that
-        another part holds under the canonical name ``tied_to`` (the embedding table)."""
+        another part holds under the canonical name ``tied_to`` (the embedding table).  ``name``:
+        what the head's own weight is called in a checkpoint, after the part's prefix."""
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
         self.tied_to = tied_to
+        self.name = name
         self._tied_weight = None
         self.proj = None
 
     def tensor_specs(self):
-        return (TensorSpec("weight", (self.vocab_size, self.hidden_size), optional=self.tied),)
+        return (TensorSpec(self.name, (self.vocab_size, self.hidden_size), optional=self.tied),)
 
     def imports(self):
         return (self.tied_to,) if self.tied else ()
@@ -58,8 +98,8 @@ class LinearHead(Part):
         self._tied_weight = tensors.get(self.tied_to)
 
     def load(self, tensors, device, dtype):
-        if "weight" in tensors:      # an explicit head wins over the tie
-            self.proj = Linear(tensors["weight"].to(device=device, dtype=dtype).contiguous())
+        if self.name in tensors:     # an explicit head wins over the tie
+            self.proj = Linear(tensors[self.name].to(device=device, dtype=dtype).contiguous())
         elif self.tied and self._tied_weight is not None:
             if tuple(self._tied_weight.shape) != (self.vocab_size, self.hidden_size):
                 raise ValueError(f"output head is tied to {self.tied_to}, whose shape {tuple(self._tied_weight.shape)} "

@@ -4,6 +4,8 @@ product feeds the activation; in the decode kernel the activation is its epilogu
 
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from ..ops import kernels, linear
@@ -57,3 +59,84 @@ class SwiGLU(FeedForward):
             else:
                 kernels.silu_mul(self.gate_up_proj(h), act, self.paired)
         return self.down_proj(act, residual=residual)
+
+
+@register_feed_forward("routed_glu")
+class RoutedGLU(FeedForward):
+    """A mixture of ``experts`` small gated feed-forwards of which each token uses ``top``, plus an
+    optional shared one that every token uses.
+
+    Router: ``z = Wr h`` in float32, scores ``sigmoid(z)``; the ``top`` largest are chosen and weigh
+    in with their scores as they are (not renormalised).  The weight multiplies the expert's
+    *input*: the routed part is the sum of ``expert(s_e * h)``.  An expert has no biases:
+    ``g = min(Wg a, limit)``, ``u = clamp(Wu a, -limit, limit)``, ``Wd (g * sigmoid(alpha g) * (u + 1))``.
+    The shared expert has the same form with sizes and limit of its own; its result is multiplied
+    by ``sigmoid(wsg . h)``, one number per token.
+
+    The pairs of a step are sorted by expert on the device and two grouped products walk them
+    (``csrc/moe.cu``); the host reads nothing back, so a step of single tokens can be captured."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, limit: float, alpha: float = 1.702,
+                 shared_size: Optional[int] = None, shared_limit: Optional[float] = None):
+        self.hidden_size, self.experts, self.top, self.expert_size = int(hidden_size), int(experts), int(top), int(expert_size)
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.shared_size = None if not shared_size else int(shared_size)
+        self.shared_limit = self.limit if shared_limit is None else float(shared_limit)
+        if not 1 <= self.top <= min(self.experts, 16) or self.experts > 256:
+            raise ValueError(f"the router takes up to 256 experts and chooses 1 to 16 of them, got {experts} and {top}")
+
+    def tensor_specs(self):
+        h, f = self.hidden_size, self.expert_size
+        specs = []
+        for e in range(self.experts):
+            specs += [TensorSpec(f"e{e}.gate", (f, h)), TensorSpec(f"e{e}.up", (f, h)), TensorSpec(f"e{e}.down", (h, f))]
+        specs.append(TensorSpec("router", (self.experts, h), "matrix_wide"))
+        if self.shared_size:
+            s = self.shared_size
+            specs += [TensorSpec("shared.gate", (s, h)), TensorSpec("shared.up", (s, h)), TensorSpec("shared.down", (h, s)),
+                      TensorSpec("shared.sg", (1, h))]
+        return tuple(specs)
+
+    def load(self, tensors, device, dtype):
+        stack = lambda what: torch.stack([tensors[f"e{e}.{what}"] for e in range(self.experts)]).to(device=device, dtype=dtype).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        self.router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
+        self.shared_gate = self.shared_gate_up = self.shared_down = None
+        if self.shared_size:
+            gu = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0)
+            self.shared_gate_up = Linear(gu.to(device=device, dtype=dtype).contiguous())
+            self.shared_down = Linear(tensors["shared.down"].to(device=device, dtype=dtype).contiguous())
+            self.shared_gate = tensors["shared.sg"].reshape(-1).to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, ctx, h):
+        n, top, experts = h.shape[0], self.top, self.experts
+        pairs = n * top
+        tile = 16 if pairs <= 16 * experts else 64          # rows of a tile of the grouped products; from the step's shape alone
+        rows = kernels.moe_max_rows(pairs, experts, tile)
+        dev = h.device
+        shared = None
+        if self.shared_size:
+            act = torch.empty((n, self.shared_size), dtype=ctx.dtype, device=dev)
+            kernels.glu_clamped(self.shared_gate_up(h), act, self.shared_limit, self.alpha)
+            shared = self.shared_down(act)
+        # counts | cursor (zero) | plan | row of every pair | pair of every row
+        n_plan = 2 + experts + rows // tile
+        ints = torch.zeros(2 * experts + n_plan + pairs + rows, dtype=torch.int32, device=dev)
+        counts, cursor = ints[:experts], ints[experts:2 * experts]
+        plan = ints[2 * experts:2 * experts + n_plan]
+        pair_row = ints[2 * experts + n_plan:2 * experts + n_plan + pairs]
+        row_pair = ints[2 * experts + n_plan + pairs:]
+        topk_idx = torch.empty((n, top), dtype=torch.int32, device=dev)
+        topk_w = torch.empty((n, top), dtype=torch.float32, device=dev)
+        sg = torch.empty(n, dtype=torch.float32, device=dev) if self.shared_size else None
+        kernels.moe_route(h, self.router, self.shared_gate, top, topk_idx, topk_w, sg, counts)
+        kernels.moe_sort(topk_idx, counts, cursor, plan, row_pair, pair_row, experts, tile)
+        act = torch.empty((rows, self.expert_size), dtype=ctx.dtype, device=dev)
+        kernels.moe_gate_up(h, self.w_gate, self.w_up, act, plan, row_pair, topk_w, top, self.limit, self.alpha, tile)
+        y = torch.empty((rows, self.hidden_size), dtype=torch.float32, device=dev)
+        kernels.moe_down(act, self.w_down, y, plan, row_pair, pairs, top, tile)
+        out = torch.empty((n, self.hidden_size), dtype=ctx.dtype, device=dev)
+        kernels.moe_combine(y, pair_row, sg, shared, out, top)
+        return out

@@ -1,7 +1,9 @@
 """RMS normalisation fused with the residual update.
 
 Formula (reference src/qwen25vl_lite/layers.py:27-31): ``x * rsqrt(mean(x^2) + eps) * w``,
-statistics in float32, plain (not 1 + w) weight.
+statistics in float32, plain (not 1 + w) weight.  With ``groups`` > 1 the vector is cut into
+that many equal consecutive parts and each is divided by its own root mean square; the weight
+spans the whole vector.
 """
 
 from __future__ import annotations
@@ -10,32 +12,48 @@ import torch
 
 from ..ops import kernels
 from ..ops.linear import DeferredNorm
-from .base import Norm, TensorSpec, register_norm
+from .base import Norm, PendingUpdate, TensorSpec, register_norm
 
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
-    def __init__(self, dim: int, eps: float):
+    def __init__(self, dim: int, eps: float, groups: int = 1, name: str = "weight"):
+        """``name``: what the weight is called in a checkpoint, after the part's prefix."""
         self.dim = int(dim)
         self.eps = float(eps)
+        self.groups = int(groups)
+        if self.groups < 1 or self.dim % self.groups:
+            raise ValueError(f"a norm over {self.dim} channels cannot be cut into {groups} equal groups")
+        self.name = name
         self.weight = None
 
     def tensor_specs(self):
-        return (TensorSpec("weight", (self.dim,), init="norm"),)
+        return (TensorSpec(self.name, (self.dim,), init="norm"),)
 
     def load(self, tensors, device, dtype):
-        self.weight = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
+        self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
 
     def forward(self, ctx, x, delta, rows=None, defer=False):
         """``defer``: the caller's consumer can normalise inside its own kernel; when nothing
         has to be added first and the step is small enough for that kernel, no kernel is
-        launched here and a ``DeferredNorm`` is returned instead of the activation."""
-        if (defer and delta is None and rows is None and ctx.dtype == torch.bfloat16
+        launched here and a ``DeferredNorm`` is returned instead of the activation.
+        ``delta`` may be a ``PendingUpdate``: it is normalised by its own norm on its way into x."""
+        post = None
+        if isinstance(delta, PendingUpdate):
+            post, delta = delta.norm, delta.value
+        plain = self.groups == 1 and post is None
+        if (defer and plain and delta is None and rows is None and ctx.dtype == torch.bfloat16
                 and x.shape[0] <= kernels.SKINNY_MAX_ROWS):
             return DeferredNorm(x, self.weight, self.eps, ctx.dtype)
         n_out = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n_out, self.dim), dtype=ctx.dtype, device=x.device)
-        kernels.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+        if plain:
+            kernels.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+        else:
+            if post is not None and not isinstance(post, RMSNorm):
+                raise TypeError("a pending update can be normalised by an rmsnorm only")
+            kernels.add_norm_groups(x, delta, None if post is None else post.weight, 0.0 if post is None else post.eps,
+                                    1 if post is None else post.groups, self.weight, self.eps, self.groups, out, rows)
         return out

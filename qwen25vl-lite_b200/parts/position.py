@@ -104,3 +104,25 @@ class MRope(PositionEncoding):
         else:
             kernels.rope_store(qkv, ctx.positions, self.inv_freq, self.axis, kv.k_pages, kv.v_pages, kv.kv_slot,
                                nq, nkv, head_dim, kv.page_size, angles)
+
+
+@register_position_encoding("token_index")
+class TokenIndex(PositionEncoding):
+    """A token's position is its index in the request, on one axis, and nothing is done to queries
+    and keys: a model whose positions enter elsewhere (a learned vector at the embedding, a bias on
+    the attention scores).  ``rotate_and_store`` only writes the step's keys and values."""
+
+    graph_safe = True
+    axes = 1
+    default_is_linear = True
+
+    def __init__(self, limit=None):
+        """``limit``: how many positions the model can place (a table of learned vectors ends there)."""
+        self.limit = None if limit is None else int(limit)
+
+    def default_positions(self, start: int, count: int, offset: int):
+        return np.arange(start + offset, start + offset + count, dtype=np.int64)[None, :]
+
+    def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
+        if kv is not None:
+            kernels.rope_store(qkv, None, None, None, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, head_dim, kv.page_size)

@@ -24,9 +24,17 @@ STD = 0.02
 
 
 def _draw(ts, gen: torch.Generator, device) -> torch.Tensor:
+    """``matrix``, ``bias``: N(0, std); ``norm``: 1 + N(0, std); ``matrix_wide``: N(0, 10 std), for
+    small matrices whose products should not all be near zero (routers, gates of a recurrence);
+    ``positive``: uniform in [0.05, 1); ``fraction``: uniform in [0.2, 0.8)."""
+    if ts.init in ("positive", "fraction"):
+        t = torch.rand(ts.shape, generator=gen, dtype=torch.float32, device=device)
+        return t * 0.95 + 0.05 if ts.init == "positive" else t * 0.6 + 0.2
     t = torch.randn(ts.shape, generator=gen, dtype=torch.float32, device=device) * STD
     if ts.init == "norm":
         t += 1.0
+    elif ts.init == "matrix_wide":
+        t *= 10.0
     return t
 
 
@@ -81,7 +89,7 @@ def load_random_model(config_json: Dict[str, Any], seed: int, dtype: str = "bflo
     def get_tensor(name: str) -> torch.Tensor:
         ts = expected[name]
         t = _draw(ts, gen, device)
-        return t if ts.init != "matrix" else t.to(target)
+        return t if ts.init not in ("matrix", "matrix_wide") else t.to(target)
 
     model.load(get_tensor, names, device, target)
     return cfg, model
