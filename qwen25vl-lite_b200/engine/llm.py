@@ -34,6 +34,9 @@ class LLM:
             self.config, self.model = load_random_model(random_config, weights_seed, self.ecfg.dtype, self.ecfg.device)
         else:
             raise ValueError("LLM needs a model folder or a random_config")
+        limit = getattr(self.model.position, "limit", None)
+        if limit is not None:                       # the model places no token beyond its last position
+            self.ecfg.max_model_len = min(self.ecfg.max_model_len, limit)
         self.runner = ModelRunner(self.model, self.ecfg.num_blocks, self.ecfg.block_size, self.ecfg.max_num_seqs,
                                   max_step_tokens=self.ecfg.max_num_batched_tokens, cuda_graphs=self.ecfg.cuda_graph)
         self.sampler = Sampler(self.ecfg.device)

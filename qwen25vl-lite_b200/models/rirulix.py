@@ -22,14 +22,17 @@ def build_spec(cfg: RirulixConfig) -> ModelSpec:
     h = cfg.hidden_size
     norm = lambda name: PartSpec("rmsnorm", dict(dim=h, eps=cfg.norm_eps, groups=cfg.norm_groups, name=name))
     layers = []
-    seen_value_source = False
+    value_source = None                 # (kv heads, value size) of the first layer that mixes values
     for i, layer in enumerate(cfg.layers):
         m = layer.mixer
         if layer.type == "attention":
             value_mix = None
             if m.v_mix:
-                value_mix = "follower" if seen_value_source else "source"
-                seen_value_source = True
+                value_mix = "follower" if value_source else "source"
+                if value_source and value_source != (m.kv_heads, m.vdim):
+                    raise ValueError(f"layers[{i}] mixes its values ({m.kv_heads} heads of {m.vdim}) with those of the first "
+                                     f"such layer, which has {value_source[0]} heads of {value_source[1]}")
+                value_source = value_source or (m.kv_heads, m.vdim)
             mixer = PartSpec("biased_window_attention", dict(
                 hidden_size=h, num_heads=m.heads, num_kv_heads=m.kv_heads, head_dim=m.dim, value_dim=m.vdim, scale=m.scale,
                 window=m.window, keep_first=m.keep_first, distance_bias=True, value_mix=value_mix), "mix.")
