@@ -185,3 +185,396 @@ Q25_EXPORT int q25_kv_store_mix_bf16(void* qkv, int qs, const void* vo, int ldo,
                                      int nq, int nkv, int dk, int dv, int ps, void* s) {
   return kv_store_mix<bf16>(qkv, qs, vo, ldo, mix, kp, vp, slot, n, nq, nkv, dk, dv, ps, s);
 }
+
+// ================================================================================================
+// The bfloat16 tensor-core kernels (mma.sync m16n8k16, float accumulators), FlashAttention-style over
+// the pages, for key sizes DK and value sizes DV that are multiples of 16 up to 128.
+//
+// The keys a piece of work walks are a list of 64-key (runs) or 32-key (single tokens) tiles: first
+// the tiles of the kept first tokens that the window has left behind, then the tiles from the
+// window's start to the last query; every score is masked by the rule itself (j <= i and (i - j <
+// window or j < keep_first)), and a tile of kept tokens counts only keys below keep_first, so no key
+// counts twice.  Scores stay in float in the base-2 domain: s = q.k * scale * log2(e) - r1 *
+// log2(1 + r2 * (i - j)), one lg2 per score; probabilities are rounded to bfloat16 for P.V only.
+//
+// Runs: a CTA of 4 warps takes 64 rows of (token, head of the kv group) pairs of one entry and one
+// kv head; all warps share the key tiles (two stages of cp.async).  Single tokens: the 4 warps of a
+// CTA all hold the token's heads (up to 16) and take the key tiles of their key range in turn, each
+// warp with a two-stage pipeline of its own; they merge through shared memory; with more than one
+// key range per token (long contexts) the ranges leave (max, sum, unnormalised output) in scratch
+// memory and a second kernel adds them up in order.
+// ================================================================================================
+#include "attention_decode.cuh"
+
+struct BiasedArgs {
+  const bf16* qkv;
+  int qkv_stride;
+  bf16* out;
+  const bf16* kpages;
+  const bf16* vpages;
+  const int* block_table;
+  int table_width;
+  const int* cu_q;
+  const int* q_start_pos;
+  const int* items;  // runs: (entry, row tile) pairs; single tokens: entry indices
+  int nq, nkv, page_size, window, keep_first;
+  float scale_log2;
+  const float* r1;
+  const float* r2;
+  int n_splits;
+  float* part_o;   // [items, nq, splits, DV]
+  float* part_ml;  // [items, nq, splits, 2]
+};
+
+// The tiles of keys that queries at positions p_first .. p_last walk.
+struct KeyWalk {
+  int kept, lo, hi, sink_tiles, win_key0, n_tiles;
+  __device__ __forceinline__ void set(int p_first, int p_last, int window, int keep_first, int bn) {
+    lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    if (lo <= keep_first) lo = 0;
+    kept = lo > 0 ? keep_first : 0;
+    hi = p_last;
+    sink_tiles = (kept + bn - 1) / bn;
+    win_key0 = lo / bn * bn;
+    n_tiles = sink_tiles + (hi - win_key0) / bn + 1;
+  }
+  // first key of tile i, and the range of keys [rl, rh] that count in it
+  __device__ __forceinline__ void tile(int i, int bn, int& key0, int& rl, int& rh) const {
+    if (i < sink_tiles) { key0 = i * bn; rl = 0; rh = kept - 1; }
+    else { key0 = win_key0 + (i - sink_tiles) * bn; rl = lo; rh = hi; }
+  }
+};
+
+// Copies keys [key0, key0 + BN) of one kv head into K and V tiles (zeros past `last`), by NT threads.
+template <int DK, int DV, int BN, int NT>
+__device__ __forceinline__ void biased_load_tile(unsigned char* ks, unsigned char* vs, const BiasedArgs& a, const int* table, int kvh,
+                                                 int key0, int last, int tid) {
+  constexpr int CK = DK / 8, CV = DV / 8;
+  for (int idx = tid; idx < BN * (CK + CV); idx += NT) {
+    const bool is_k = idx < BN * CK;
+    const int j = is_k ? idx : idx - BN * CK;
+    const int key = is_k ? j / CK : j / CV, ch = is_k ? j % CK : j % CV;
+    const int kidx = key0 + key;
+    const bool valid = kidx <= last;
+    const int kc = valid ? kidx : last;
+    const int page = table[kc / a.page_size];
+    const size_t row = ((size_t)page * a.nkv + kvh) * a.page_size + kc % a.page_size;
+    if (is_k) cp_async16(ks + key * Tile<DK>::PITCH + ch * 16, a.kpages + row * DK + ch * 8, valid);
+    else cp_async16(vs + key * Tile<DV>::PITCH + ch * 16, a.vpages + row * DV + ch * 8, valid);
+  }
+}
+
+// One tile of keys for the warp's 16 rows.  p0/p1: positions of rows g and g+8 (-1: no such row);
+// b1x/b2x: the bias numbers of the rows' heads; [rl, rh]: the keys of the tile that count.
+template <int DK, int DV, int BN>
+__device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], const unsigned char* ks, const unsigned char* vs,
+                                            int key0, int rl, int rh, int p0, int p1, int window, int keep_first, float scale_log2,
+                                            float b10, float b20, float b11, float b21, float (&m)[2], float (&l)[2],
+                                            float (&o)[DV / 8][4]) {
+  constexpr int PK = Tile<DK>::PITCH, PV = Tile<DV>::PITCH;
+  const int lane = threadIdx.x & 31, t = lane & 3;
+  float s[BN / 8][4];
+#pragma unroll
+  for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < DK / 16; ++kk) {
+    unsigned b[BN / 8][2];
+#pragma unroll
+    for (int j = 0; j < BN / 8; ++j) ldmatrix_x2(b[j], ks + (j * 8 + (lane & 7)) * PK + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2);
+#pragma unroll
+    for (int j = 0; j < BN / 8; ++j) mma_bf16(s[j], qf[kk], b[j][0], b[j][1]);
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int kidx = key0 + j * 8 + 2 * t + (e & 1);
+      const int p = e < 2 ? p0 : p1;
+      const int dist = p - kidx;
+      const bool ok = kidx >= rl && kidx <= rh && dist >= 0 && (window <= 0 || dist < window || kidx < keep_first);
+      const float b1 = e < 2 ? b10 : b11, b2 = e < 2 ? b20 : b21;
+      s[j][e] = ok ? fmaf(s[j][e], scale_log2, -b1 * __log2f(fmaf(b2, (float)dist, 1.0f))) : -INFINITY;
+    }
+    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+  const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;  // nothing seen yet
+  const float c0 = exp2f(m[0] - ms0), c1 = exp2f(m[1] - ms1);
+  m[0] = mn0;
+  m[1] = mn1;
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < BN / 8; ++j) {
+    s[j][0] = exp2f(s[j][0] - ms0);
+    s[j][1] = exp2f(s[j][1] - ms0);
+    s[j][2] = exp2f(s[j][2] - ms1);
+    s[j][3] = exp2f(s[j][3] - ms1);
+    sum0 += s[j][0] + s[j][1];
+    sum1 += s[j][2] + s[j][3];
+  }
+  l[0] = l[0] * c0 + sum0;  // per-thread partial sums; the quad is reduced once at the end
+  l[1] = l[1] * c1 + sum1;
+#pragma unroll
+  for (int nb = 0; nb < DV / 8; ++nb) {
+    o[nb][0] *= c0;
+    o[nb][1] *= c0;
+    o[nb][2] *= c1;
+    o[nb][3] *= c1;
+  }
+#pragma unroll
+  for (int kk = 0; kk < BN / 16; ++kk) {
+    unsigned pa[4];
+    pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    const unsigned char* vrow = vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * PV;
+#pragma unroll
+    for (int np = 0; np < DV / 16; ++np) {
+      unsigned b[4];
+      ldmatrix_x4_trans(b, vrow + (np * 16 + 8 * (lane >> 4)) * 2);
+      mma_bf16(o[2 * np], pa, b[0], b[1]);
+      mma_bf16(o[2 * np + 1], pa, b[2], b[3]);
+    }
+  }
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int BN = 64, KT = BN * Tile<DK>::PITCH, VT = BN * Tile<DV>::PITCH;
+  extern __shared__ __align__(16) unsigned char smem[];     // two stages of (K tile, V tile)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int entry = a.items[2 * blockIdx.x], row_tile = a.items[2 * blockIdx.x + 1];
+  const int kvh = blockIdx.y;
+  const int group = a.nq / a.nkv;
+  const int first = a.cu_q[entry], n = a.cu_q[entry + 1] - first, start = a.q_start_pos[entry];
+  const int rows = n * group;
+  const int tile_row0 = row_tile * 64;
+  const int t_first = tile_row0 / group, t_last = min(tile_row0 + 63, rows - 1) / group;
+  KeyWalk walk;
+  walk.set(start + t_first, start + t_last, a.window, a.keep_first, BN);
+  const int* table = a.block_table + (size_t)entry * a.table_width;
+  // this thread's two rows
+  const int r0 = tile_row0 + warp * 16 + g, r1 = r0 + 8;
+  const int tok0 = r0 < rows ? r0 / group : -1, tok1 = r1 < rows ? r1 / group : -1;
+  const int h0 = kvh * group + (r0 < rows ? r0 % group : 0), h1 = kvh * group + (r1 < rows ? r1 % group : 0);
+  const int p0 = tok0 < 0 ? -1 : start + tok0, p1 = tok1 < 0 ? -1 : start + tok1;
+  const float b10 = a.r1 ? a.r1[h0] : 0.f, b20 = a.r1 ? a.r2[h0] : 0.f, b11 = a.r1 ? a.r1[h1] : 0.f, b21 = a.r1 ? a.r2[h1] : 0.f;
+  unsigned qf[DK / 16][4];
+  load_q<DK>(qf, [&](int r) -> const bf16* {
+    const int rr = tile_row0 + warp * 16 + r;
+    return rr < rows ? a.qkv + (size_t)(first + rr / group) * a.qkv_stride + (size_t)(kvh * group + rr % group) * DK : nullptr;
+  });
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  int key0, rl, rh;
+  walk.tile(0, BN, key0, rl, rh);
+  biased_load_tile<DK, DV, BN, 128>(smem, smem + KT, a, table, kvh, key0, walk.hi, threadIdx.x);
+  cp_async_commit();
+  for (int i = 0; i < walk.n_tiles; ++i) {
+    unsigned char* cur = smem + (i & 1) * (KT + VT);
+    if (i + 1 < walk.n_tiles) {
+      int nk0, nrl, nrh;
+      walk.tile(i + 1, BN, nk0, nrl, nrh);
+      unsigned char* nxt = smem + ((i + 1) & 1) * (KT + VT);
+      biased_load_tile<DK, DV, BN, 128>(nxt, nxt + KT, a, table, kvh, nk0, walk.hi, threadIdx.x);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    walk.tile(i, BN, key0, rl, rh);
+    biased_tile<DK, DV, BN>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+    __syncthreads();
+  }
+  const float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
+  const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+#pragma unroll
+  for (int nb = 0; nb < DV / 8; ++nb) {
+    const int c = nb * 8 + 2 * t;
+    if (tok0 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok0) * a.nq * DV + (size_t)h0 * DV + c) = pack_bf16(o[nb][0] * i0, o[nb][1] * i0);
+    if (tok1 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok1) * a.nq * DV + (size_t)h1 * DV + c) = pack_bf16(o[nb][2] * i1, o[nb][3] * i1);
+  }
+}
+
+// Single tokens: blockIdx.x = item, blockIdx.y = kv head, blockIdx.z = key range.
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int BN = 32, KT = BN * Tile<DK>::PITCH, VT = BN * Tile<DV>::PITCH, WARP_BYTES = 2 * (KT + VT);
+  constexpr int SLAB = DV + 4;                               // floats per merged row
+  extern __shared__ __align__(16) unsigned char smem[];     // per warp two stages of (K, V); reused for the merge
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int entry = a.items[item];
+  const int group = a.nq / a.nkv;
+  const int token = a.cu_q[entry], p = a.q_start_pos[entry];
+  KeyWalk walk;
+  walk.set(p, p, a.window, a.keep_first, BN);
+  const int per = (walk.n_tiles + a.n_splits - 1) / a.n_splits;
+  const int t_begin = split * per, t_end = min(walk.n_tiles, t_begin + per);
+  const int* table = a.block_table + (size_t)entry * a.table_width;
+  const int h0 = kvh * group + (g < group ? g : 0), h1 = kvh * group + (g + 8 < group ? g + 8 : 0);
+  const int p0 = g < group ? p : -1, p1 = g + 8 < group ? p : -1;
+  const float b10 = a.r1 ? a.r1[h0] : 0.f, b20 = a.r1 ? a.r2[h0] : 0.f, b11 = a.r1 ? a.r1[h1] : 0.f, b21 = a.r1 ? a.r2[h1] : 0.f;
+  unsigned qf[DK / 16][4];
+  load_q<DK>(qf, [&](int r) -> const bf16* {
+    return r < group ? a.qkv + (size_t)token * a.qkv_stride + (size_t)(kvh * group + r) * DK : nullptr;
+  });
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  unsigned char* mine = smem + warp * WARP_BYTES;
+  int key0, rl, rh;
+  int i = t_begin + warp;
+  if (i < t_end) {
+    walk.tile(i, BN, key0, rl, rh);
+    biased_load_tile<DK, DV, BN, 32>(mine, mine + KT, a, table, kvh, key0, walk.hi, lane);
+  }
+  cp_async_commit();
+  for (int stage = 0; i < t_end; i += 4, stage ^= 1) {
+    unsigned char* cur = mine + stage * (KT + VT);
+    if (i + 4 < t_end) {
+      int nk0, nrl, nrh;
+      walk.tile(i + 4, BN, nk0, nrl, nrh);
+      unsigned char* nxt = mine + (stage ^ 1) * (KT + VT);
+      biased_load_tile<DK, DV, BN, 32>(nxt, nxt + KT, a, table, kvh, nk0, walk.hi, lane);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncwarp();
+    walk.tile(i, BN, key0, rl, rh);
+    biased_tile<DK, DV, BN>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  __syncthreads();                                           // every warp is done with its tiles
+  // the warps' (max, sum, output) side by side, then each thread merges some (row, column) pairs
+  float* ml = reinterpret_cast<float*>(smem);                // [4 warps][16 rows][2]
+  float* slab = ml + 4 * 16 * 2;                             // [4 warps][16 rows][SLAB]
+  const float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
+  if (t == 0) {
+    ml[(warp * 16 + g) * 2] = m[0]; ml[(warp * 16 + g) * 2 + 1] = l0;
+    ml[(warp * 16 + g + 8) * 2] = m[1]; ml[(warp * 16 + g + 8) * 2 + 1] = l1;
+  }
+#pragma unroll
+  for (int nb = 0; nb < DV / 8; ++nb) {
+    const int c = nb * 8 + 2 * t;
+    slab[(warp * 16 + g) * SLAB + c] = o[nb][0];
+    slab[(warp * 16 + g) * SLAB + c + 1] = o[nb][1];
+    slab[(warp * 16 + g + 8) * SLAB + c] = o[nb][2];
+    slab[(warp * 16 + g + 8) * SLAB + c + 1] = o[nb][3];
+  }
+  __syncthreads();
+  for (int x = threadIdx.x; x < group * DV; x += 128) {
+    const int r = x / DV, c = x % DV;
+    float mm = -INFINITY;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, ml[(w * 16 + r) * 2]);
+    float sum = 0.f, acc = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float mw = ml[(w * 16 + r) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+      sum = fmaf(ml[(w * 16 + r) * 2 + 1], f, sum);
+      acc = fmaf(slab[(w * 16 + r) * SLAB + c], f, acc);
+    }
+    const int head = kvh * group + r;
+    if (a.n_splits == 1) {
+      a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+    } else {
+      const size_t at = ((size_t)item * a.nq + head) * a.n_splits + split;
+      a.part_o[at * DV + c] = acc;
+      if (c == 0) { a.part_ml[at * 2] = mm; a.part_ml[at * 2 + 1] = sum; }
+    }
+  }
+}
+
+// Adds the key ranges of a token's head up, in order.  One block per (item, head), DV threads.
+template <int DV>
+__global__ void biased_combine_kernel(BiasedArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const int item = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
+  const int token = a.cu_q[a.items[item]];
+  const size_t base = ((size_t)item * a.nq + head) * a.n_splits;
+  float mm = -INFINITY;
+  for (int s = 0; s < a.n_splits; ++s) mm = fmaxf(mm, a.part_ml[(base + s) * 2]);
+  float sum = 0.f, acc = 0.f;
+  for (int s = 0; s < a.n_splits; ++s) {
+    const float ms = a.part_ml[(base + s) * 2];
+    const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+    sum = fmaf(a.part_ml[(base + s) * 2 + 1], f, sum);
+    acc = fmaf(a.part_o[(base + s) * DV + c], f, acc);
+  }
+  a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+}
+
+template <int DK, int DV>
+static int biased_mma_launch(const BiasedArgs& a, int n_tiles, int n_items, const int* tiles, const int* items, cudaStream_t s) {
+  if (n_tiles > 0) {
+    constexpr int SMEM = 2 * 64 * (Tile<DK>::PITCH + Tile<DV>::PITCH);
+    if (SMEM > 48 * 1024) {
+      const cudaError_t e = cudaFuncSetAttribute(biased_prefill_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+      if (e != cudaSuccess) return (int)e;
+    }
+    BiasedArgs b = a;
+    b.items = tiles;
+    launch(biased_prefill_kernel<DK, DV>, dim3(n_tiles, a.nkv), dim3(128), SMEM, s, b);
+  }
+  if (n_items > 0) {
+    constexpr int TILES = 4 * 2 * 32 * (Tile<DK>::PITCH + Tile<DV>::PITCH), MERGE = (4 * 16 * 2 + 4 * 16 * (DV + 4)) * 4;
+    constexpr int SMEM = TILES > MERGE ? TILES : MERGE;
+    if (SMEM > 48 * 1024) {
+      const cudaError_t e = cudaFuncSetAttribute(biased_decode_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+      if (e != cudaSuccess) return (int)e;
+    }
+    BiasedArgs b = a;
+    b.items = items;
+    launch(biased_decode_kernel<DK, DV>, dim3(n_items, a.nkv, a.n_splits), dim3(128), SMEM, s, b);
+    if (a.n_splits > 1) launch(biased_combine_kernel<DV>, dim3(n_items, a.nq), dim3(DV), 0, s, b);
+  }
+  return launch_status();
+}
+
+// Sizes the tensor-core kernels are built for: keys and values of 32, 64 or 128 channels.
+Q25_EXPORT int q25_biased_attention_mma_supports(int dk, int dv) {
+  const bool k = dk == 32 || dk == 64 || dk == 128, v = dv == 32 || dv == 64 || dv == 128;
+  return k && v ? 1 : 0;
+}
+
+// tiles: (entry, row tile of 64 rows) pairs of the runs; items: the entries of one token (groups of
+// up to 16 query heads).  n_splits key ranges per single token; scratch as biased_decode_kernel says.
+Q25_EXPORT int q25_biased_attention_mma_bf16(const void* qkv, int qkv_stride, void* out, const void* kp, const void* vp, const int* bt,
+                                             int tw, const int* cu, const int* sp, const int* tiles, int n_tiles, const int* items,
+                                             int n_items, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
+                                             const float* r1, const float* r2, int n_splits, float* part_o, float* part_ml, void* stream) {
+  if (n_tiles <= 0 && n_items <= 0) return 0;
+  if (nkv <= 0 || nq % nkv || ps <= 0 || n_splits < 1 || (n_items > 0 && nq / nkv > 16)) return (int)cudaErrorInvalidValue;
+  BiasedArgs a;
+  a.qkv = (const bf16*)qkv; a.qkv_stride = qkv_stride; a.out = (bf16*)out; a.kpages = (const bf16*)kp; a.vpages = (const bf16*)vp;
+  a.block_table = bt; a.table_width = tw; a.cu_q = cu; a.q_start_pos = sp; a.items = nullptr;
+  a.nq = nq; a.nkv = nkv; a.page_size = ps; a.window = window; a.keep_first = keep;
+  a.scale_log2 = scale * 1.4426950408889634f; a.r1 = r1; a.r2 = r2; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
+  cudaStream_t s = (cudaStream_t)stream;
+#define BIASED_CASE(K, V) if (dk == K && dv == V) return biased_mma_launch<K, V>(a, n_tiles, n_items, tiles, items, s);
+  BIASED_CASE(32, 32) BIASED_CASE(32, 64) BIASED_CASE(32, 128)
+  BIASED_CASE(64, 32) BIASED_CASE(64, 64) BIASED_CASE(64, 128)
+  BIASED_CASE(128, 32) BIASED_CASE(128, 64) BIASED_CASE(128, 128)
+#undef BIASED_CASE
+  return (int)cudaErrorInvalidValue;
+}

@@ -17,7 +17,7 @@
 // Every output element of the plain products is one FMA chain over k in order, whatever tile the
 // row falls into, so a token's result does not depend on the batch.  The bfloat16 products run on
 // the tensor cores (mma.sync m16n8k16, float accumulators) with the same layout.
-#include "common.cuh"
+#include "attention_decode.cuh"
 
 #define MOE_MAX_EXPERTS 256
 #define MOE_MAX_TOP 16
@@ -201,6 +201,117 @@ moe_grouped_fma_kernel(const T* __restrict__ A, const T* __restrict__ W0, const 
   }
 }
 
+// The grouped products on the tensor cores (bfloat16, mma.sync m16n8k16, float accumulators): a CTA
+// of 4 warps takes a tile of BM rows x 64 columns of one expert; with BM = 64 a warp holds 16 rows and
+// all 64 columns, with BM = 16 all rows and 16 columns.  K is walked in steps of 32: the weights'
+// rows by 16-byte cp.async, the rows of A by plain loads (gate and up: the token's row times its
+// weight, rounded to bfloat16), one stage: several CTAs share an SM and hide each other's loads.
+// Every element's sum runs over K in the same order whatever tile the row is in.
+template <bool GATE_UP, int BM>
+__global__ void __launch_bounds__(128)
+moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, const bf16* __restrict__ W1, void* __restrict__ out_,
+                       const int* __restrict__ plan, const int* __restrict__ row_pair, const float* __restrict__ topk_w,
+                       int experts, int top, int N, int K, float limit, float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int BN = 64, BK = 32, P = BK * 2 + 16;            // pitch in bytes: an odd number of 16-byte chunks
+  constexpr int WN = BM == 64 ? 64 : 16;                      // columns a warp holds
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int e = plan[2 + experts + tile];
+  __shared__ __align__(16) unsigned char As[BM * P];
+  __shared__ __align__(16) unsigned char Ws0[BN * P];
+  __shared__ __align__(16) unsigned char Ws1[GATE_UP ? BN * P : 16];
+  __shared__ int src_row[BM];
+  __shared__ float src_w[BM];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int m0 = tile * BM, n0 = blockIdx.x * BN;
+  for (int r = threadIdx.x; r < BM; r += 128) {
+    const int pair = row_pair[m0 + r];
+    src_row[r] = pair < 0 ? -1 : (GATE_UP ? pair / top : m0 + r);
+    src_w[r] = (GATE_UP && pair >= 0) ? topk_w[pair] : 1.f;
+  }
+  __syncthreads();
+  const bf16* w0 = W0 + (size_t)e * N * K;
+  const bf16* w1 = GATE_UP ? W1 + (size_t)e * N * K : nullptr;
+  const int row_base = BM == 64 ? warp * 16 : 0, col_base = BM == 64 ? 0 : warp * 16;
+  float acc0[WN / 8][4], acc1[GATE_UP ? WN / 8 : 1][4];
+#pragma unroll
+  for (int j = 0; j < WN / 8; ++j) acc0[j][0] = acc0[j][1] = acc0[j][2] = acc0[j][3] = 0.f;
+  if (GATE_UP) {
+#pragma unroll
+    for (int j = 0; j < WN / 8; ++j) acc1[j][0] = acc1[j][1] = acc1[j][2] = acc1[j][3] = 0.f;
+  }
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int x = threadIdx.x; x < BN * (BK / 8); x += 128) {
+      const int r = x / (BK / 8), ch = x % (BK / 8);
+      const int gn = n0 + r, gk = k0 + ch * 8;
+      const bool ok = gn < N && gk < K;
+      const size_t off = ok ? (size_t)gn * K + gk : 0;
+      cp_async16(Ws0 + r * P + ch * 16, w0 + off, ok);
+      if (GATE_UP) cp_async16(Ws1 + r * P + ch * 16, w1 + off, ok);
+    }
+    cp_async_commit();
+    for (int x = threadIdx.x; x < BM * (BK / 8); x += 128) {
+      const int r = x / (BK / 8), ch = x % (BK / 8);
+      const int gk = k0 + ch * 8, src = src_row[r];
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (src >= 0 && gk < K) {
+        v = *reinterpret_cast<const uint4*>(A + (size_t)src * K + gk);
+        if (GATE_UP) {
+          const float w = src_w[r];
+          unsigned* u = reinterpret_cast<unsigned*>(&v);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&u[i]);
+            u[i] = pack_bf16(__low2float(b) * w, __high2float(b) * w);
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(As + r * P + ch * 16) = v;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK / 16; ++kk) {
+      unsigned a[4];
+      ldmatrix_x4(a, As + (row_base + (lane & 15)) * P + (kk * 16 + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int j = 0; j < WN / 8; ++j) {
+        unsigned b[2];
+        ldmatrix_x2(b, Ws0 + (col_base + j * 8 + (lane & 7)) * P + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2);
+        mma_bf16(acc0[j], a, b[0], b[1]);
+        if (GATE_UP) {
+          ldmatrix_x2(b, Ws1 + (col_base + j * 8 + (lane & 7)) * P + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2);
+          mma_bf16(acc1[j], a, b[0], b[1]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < WN / 8; ++j) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = row_base + g + 8 * half;
+      if (src_row[r] < 0) continue;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int gn = n0 + col_base + j * 8 + 2 * t + c;
+        if (gn >= N) continue;
+        const float v0 = acc0[j][2 * half + c];
+        if (GATE_UP) {
+          const float gt = fminf(v0, limit);
+          const float up = fminf(fmaxf(acc1[j][2 * half + c], -limit), limit);
+          reinterpret_cast<bf16*>(out_)[(size_t)(m0 + r) * N + gn] = __float2bfloat16_rn(gt / (1.0f + expf(-alpha * gt)) * (up + 1.0f));
+        } else {
+          reinterpret_cast<float*>(out_)[(size_t)(m0 + r) * N + gn] = v0;
+        }
+      }
+    }
+  }
+}
+
 // out[n, :] = sum over the token's choices, in their order, of y[row of the pair, :]
 //             (+ sg[n] * shared[n, :]), in T.
 template <typename T>
@@ -254,11 +365,31 @@ Q25_EXPORT int q25_moe_sort(const int* topk_idx, const int* counts, int* cursor,
   return launch_status();
 }
 
+template <bool GATE_UP>
+static int moe_grouped_mma(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
+                           const float* topk_w, int n_pairs, int experts, int top, int N, int K, float limit, float alpha, int tile,
+                           void* stream) {
+  const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
+  if (tile == 16) {
+    launch(moe_grouped_mma_kernel<GATE_UP, 16>, dim3((N + 63) / 64, tiles), dim3(128), 0, (cudaStream_t)stream, (const bf16*)A,
+           (const bf16*)W0, (const bf16*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
+  } else if (tile == 64) {
+    launch(moe_grouped_mma_kernel<GATE_UP, 64>, dim3((N + 63) / 64, tiles), dim3(128), 0, (cudaStream_t)stream, (const bf16*)A,
+           (const bf16*)W0, (const bf16*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
+  } else {
+    return (int)cudaErrorInvalidValue;
+  }
+  return launch_status();
+}
+
 template <typename T, bool GATE_UP>
 static int moe_grouped_fma(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
                            const float* topk_w, int n_pairs, int experts, int top, int N, int K, float limit, float alpha, int tile,
                            void* stream) {
   if (n_pairs <= 0) return 0;
+  // bfloat16 operands whose rows start on 16-byte boundaries go to the tensor cores
+  if (sizeof(T) == 2 && K % 8 == 0 && !(((uintptr_t)A | (uintptr_t)W0 | (uintptr_t)W1) & 15))
+    return moe_grouped_mma<GATE_UP>(A, W0, W1, out, plan, row_pair, topk_w, n_pairs, experts, top, N, K, limit, alpha, tile, stream);
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
   if (tile == 16) {
     launch(moe_grouped_fma_kernel<T, GATE_UP, 16, 64, 16, 1, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,

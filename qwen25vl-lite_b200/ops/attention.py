@@ -165,7 +165,7 @@ def _scratch_floats(n: int, device, use: str = "decode") -> torch.Tensor:
     prompt's parts must not make it move."""
     buf = _scratch.get((device, use))
     if buf is None or buf.numel() < n:
-        if buf is not None and use == "decode":
+        if buf is not None and use in ("decode", "biased"):
             _retired.append(buf)                    # a captured step may still point at it
         buf = torch.empty(max(n, 1 << 20), dtype=torch.float32, device=device)
         _scratch[(device, use)] = buf
@@ -263,8 +263,8 @@ def plan_biased(host, group: int, window: int, keep_first: int) -> Dict[str, np.
     that bring one token (``decode_items``) and (entry, row tile) pairs of the runs, a tile being
     64 consecutive (token, head of the group) rows; the tiles that walk the most keys go first."""
     q_lens, starts = host.q_lens, host.starts
-    singles = [i for i, n in enumerate(q_lens) if n == 1]
-    runs = [i for i, n in enumerate(q_lens) if n > 1]
+    singles = [i for i, n in enumerate(q_lens) if n == 1 and group <= 16]     # a warp holds 16 rows: the heads of one token
+    runs = [i for i, n in enumerate(q_lens) if n > 1 or group > 16]
 
     def keys(i, t):                     # keys the tile's last token sees
         last = starts[i] + min((t * 64 + 63) // group, q_lens[i] - 1)
@@ -280,6 +280,18 @@ def attend_biased(ctx, plan, qkv, kv, nq: int, nkv: int, dk: int, dv: int, windo
     """qkv: [N, nq*dk + nkv*dk + nkv*dv] as projected, this step's keys and values already in the
     pages.  Returns [N, nq * dv]."""
     out = torch.empty((qkv.shape[0], nq * dv), dtype=qkv.dtype, device=qkv.device)
+    window, keep_first = int(window or 0), int(keep_first or 0)
+    if kernels.biased_attention_mma_supports(qkv.dtype, dk, dv):
+        items, tiles = plan.get("decode_items"), _pairs(plan.get("tiles64"))
+        splits, scratch = 1, None
+        if items is not None:
+            visible = min(ctx.max_kv_len, window + keep_first) if window else ctx.max_kv_len
+            splits = decode_splits(items.shape[0], nkv, visible)
+            if splits > 1:
+                scratch = _scratch_floats(items.shape[0] * nq * splits * (dv + 2), qkv.device, "biased")
+        kernels.biased_attention_mma(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles, items,
+                                     nq, nkv, dk, dv, kv.page_size, window, keep_first, scale, r1, r2, splits, scratch)
+        return out
     kernels.biased_attention_generic(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.token_seq, ctx.cu_q,
                                      ctx.q_start_pos, nq, nkv, dk, dv, kv.page_size, int(window or 0), int(keep_first or 0),
                                      scale, r1, r2)

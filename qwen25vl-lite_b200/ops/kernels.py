@@ -739,6 +739,39 @@ def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torc
         page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _stream()), "biased_attention_generic")
 
 
+def biased_attention_mma_supports(dtype: torch.dtype, dk: int, dv: int) -> bool:
+    """Sizes the tensor-core kernels of this attention are built for; the rest goes to the general kernel."""
+    return dtype == torch.bfloat16 and dk in (32, 64, 128) and dv in (32, 64, 128)
+
+
+def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                         cu_q: torch.Tensor, q_start_pos: torch.Tensor, tiles: Optional[torch.Tensor], items: Optional[torch.Tensor],
+                         nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
+                         r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_splits: int = 1,
+                         scratch: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core attention (bfloat16): ``tiles`` int32 [n, 2] are (entry, tile of 64 (token, head of
+    the group) rows) of the runs, ``items`` the entries that bring one token, whose keys are cut into
+    ``n_splits`` ranges (partial results through ``scratch``, float32, len(items) * nq * n_splits * (dv + 2))."""
+    n_items = 0 if items is None else items.shape[0]
+    n_tiles = 0 if tiles is None else tiles.shape[0]
+    part_o = part_ml = 0
+    if n_items and n_splits > 1:
+        need = n_items * nq * n_splits * (dv + 2)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"biased_attention_mma: {n_splits} key ranges need {need} float32 of scratch memory")
+        part_o = scratch.data_ptr()
+        part_ml = part_o + 4 * n_items * nq * n_splits * dv
+    if not biased_attention_mma_supports(qkv.dtype, dk, dv) or (n_items and nq // nkv > 16):
+        raise KernelError(f"biased_attention_mma: unsupported sizes {dk}/{dv} or more than 16 heads per kv head for single tokens")
+    _check(_fn("q25_biased_attention_mma_bf16",
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P, _P])(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), _ptr(tiles), n_tiles, _ptr(items), n_items, nq, nkv, dk, dv,
+        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), int(n_splits), part_o, part_ml,
+        _stream()), "biased_attention_mma")
+    count_replayed((1 if n_tiles and n_items else 0) + (1 if n_items and n_splits > 1 else 0))
+
+
 # ---- the routed feed-forward ------------------------------------------------------------------------
 
 
