@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at Qwen2.5-VL sizes, random bfloat16 weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b|rirulix]
 
 One "step" is one decode step of the whole batch.  The default run (``--config 3b``) has the 3B
 layer sizes: the headline ``value`` is decoded tokens a second at batch 8 after 2,048-token
@@ -11,7 +11,8 @@ out every step).  The same line carries the 2,048-token prefill, the decode step
 decode at batch 1 and 64, the clocks seen while timing, and the number of this engine's kernel
 launches in the timed region.  ``--config 7b-trace`` runs a continuous-batching trace of 128
 requests at the 7B sizes, ``--config 32b`` decode at batch 1 / 8 / 32 after 8,192-token prompts and
-a 2,048-token prefill at the 32B sizes; each prints one line of its own.
+a 2,048-token prefill at the 32B sizes, ``--config rirulix`` prefill and decode of the Rirulix design
+at a few layer sizes beside this decoder at equal size; each prints one line of its own.
 The engine is single-GPU: for --gpus N > 1 one line says so and the exit code is 2.
 """
 
@@ -461,6 +462,76 @@ def run_7b_trace(args):
     return 0
 
 
+def _rirulix_sizes(width, layers, heads, kv_heads, dim, window, experts, top, ff, shared_ff, blocks, vocab):
+    """A Rirulix model of ``layers`` layers (two recurrent layers, then one of attention, and so on)
+    and the Qwen2.5-VL text decoder of equal size beside it: the same width, layers, heads and
+    vocabulary, a feed-forward as wide as the experts a token uses plus the shared one."""
+    attn = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True,
+                                           "mask": {"size": window, "keep_first": 4}}}
+    rec = {"type": "rglru", "mixer": {"width": width, "blocks": blocks, "conv": 4}}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
+    ours = {"architecture": "Rirulix", "vocab": vocab, "width": width, "max_positions": 8192, "norm": {"eps": 1e-6, "groups": 4},
+            "layers": [dict(attn if i % 3 == 2 else rec, mlp=mlp) for i in range(layers)]}
+    closest = _sizes(width, layers, heads, kv_heads, top * ff + shared_ff, vocab, False)
+    closest["text_config"]["rope_scaling"]["mrope_section"] = [dim // 8, 3 * dim // 16, 3 * dim // 16]
+    return ours, closest
+
+
+RIRULIX_SIZES = {
+    "w1024": _rirulix_sizes(1024, 6, 8, 2, 128, 1024, 8, 2, 1024, 1024, 8, 32000),
+    "w2048": _rirulix_sizes(2048, 6, 16, 2, 128, 1024, 16, 2, 1408, 2816, 16, 32000),
+    "w2560_d64": _rirulix_sizes(2560, 6, 40, 8, 64, 2048, 32, 4, 768, 1536, 10, 32000),
+}
+
+
+def run_rirulix(args):
+    """Prefill and decode throughput of the Rirulix design at a few layer sizes, each beside the
+    Qwen2.5-VL text decoder of equal size, random weights: a 2,048-token prompt in one step, and
+    decode steps at batch 8 and 64 after 1,024-token prompts; one JSON line."""
+    import numpy as np
+
+    from qwen25vl_lite import LLM
+    from qwen25vl_lite.engine import benchmark as B
+
+    prompt_len, decode_prompt = PROMPT_LEN, 1024
+    context = decode_prompt + args.steps + args.warmup + 64
+    clocks = ClockSampler()
+    clocks.start()
+    sizes = {}
+    launches = 0
+    for name, pair in RIRULIX_SIZES.items():
+        if args.only_size and name != args.only_size:
+            continue
+        sizes[name] = {}
+        for label, cfg in zip(("rirulix", "closest"), pair):
+            llm = LLM(random_config=cfg, weights_seed=0, dtype=args.dtype, num_blocks=64 * (-(-max(context, prompt_len) // PAGE)) + 8,
+                      block_size=PAGE, max_num_seqs=65, max_num_batched_tokens=4096, max_model_len=max(context, prompt_len),
+                      cuda_graph=not args.no_cuda_graph)
+            vocab = llm.runner.vocab_size
+            rng = np.random.default_rng(0)
+            ms = B.time_prefill(llm.runner, prompt_len, vocab, rng, warmup=3, repeats=5)
+            point = {"prefill_tokens_per_s": prompt_len / (ms / 1e3), "prefill_ms": ms, "weight_bytes": llm.model.weight_bytes()}
+            for b in (8, 64):
+                r = B.time_decode_steps(llm.runner, b, decode_prompt, args.steps, args.warmup, vocab, rng, prefill_group=4, settle_s=SETTLE_S)
+                point[f"decode_b{b}_tokens_per_s"] = r["tokens_per_s"]
+                point[f"decode_b{b}_ms_per_step"] = r["ms_per_step"]
+                launches += r["launches"]
+            sizes[name][label] = point
+            del llm
+        sizes[name]["prefill_ratio"] = sizes[name]["rirulix"]["prefill_tokens_per_s"] / sizes[name]["closest"]["prefill_tokens_per_s"]
+        sizes[name]["decode_b8_ratio"] = sizes[name]["rirulix"]["decode_b8_tokens_per_s"] / sizes[name]["closest"]["decode_b8_tokens_per_s"]
+        sizes[name]["decode_b64_ratio"] = sizes[name]["rirulix"]["decode_b64_tokens_per_s"] / sizes[name]["closest"]["decode_b64_tokens_per_s"]
+    head = sizes.get("w2048", next(iter(sizes.values())))["rirulix"]
+    print(json.dumps({"metric": "decode tokens/s, Rirulix design at width 2048 (6 layers), batch 8, 1024-token prompts",
+                      "value": head["decode_b8_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": head["decode_b8_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (seeded uniform-random token ids, random-init weights)",
+                      "config": {"model": "Rirulix, random weights", "global_batch": 8, "seq_len": context, "parallelism": "single GPU",
+                                 "l2": "weights and cache of a step exceed L2 at every size but w1024's decode"},
+                      "gpu_launches": launches, "sizes": sizes, "clocks": clocks.stop()}))
+    return 0
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -473,8 +544,10 @@ def main(argv=None):
     ap.add_argument("--only-batch", type=int, default=0, help="time decode steps at this batch size only (for profilers)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32 times the true 32-bit path of the 3b configuration (fewer --layers advised)")
-    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b"],
-                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each")
+    ap.add_argument("--only-size", default="", help="with --config rirulix: one of its sizes only (for profilers)")
+    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b", "rirulix"],
+                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each; rirulix: the "
+                         "Rirulix design at a few layer sizes beside the Qwen2.5-VL decoder of equal size")
     args = ap.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
@@ -486,7 +559,7 @@ def main(argv=None):
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm measures the 3b configuration only"}))
             return 0
         return run_reference(args)
-    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b}[args.config](args)
+    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b, "rirulix": run_rirulix}[args.config](args)
 
 
 if __name__ == "__main__":

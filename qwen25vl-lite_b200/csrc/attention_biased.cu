@@ -245,28 +245,38 @@ struct KeyWalk {
   }
 };
 
-// Copies keys [key0, key0 + BN) of one kv head into K and V tiles (zeros past `last`), by NT threads.
+// Copies keys [key0, key0 + BN) of one kv head into K and V tiles (zeros past `last`), by NT threads:
+// NT / BN threads share a key, so a thread looks one page up and takes that row's 16-byte chunks
+// (of the key and of the value) in turn.
 template <int DK, int DV, int BN, int NT>
 __device__ __forceinline__ void biased_load_tile(unsigned char* ks, unsigned char* vs, const BiasedArgs& a, const int* table, int kvh,
                                                  int key0, int last, int tid) {
-  constexpr int CK = DK / 8, CV = DV / 8;
-  for (int idx = tid; idx < BN * (CK + CV); idx += NT) {
-    const bool is_k = idx < BN * CK;
-    const int j = is_k ? idx : idx - BN * CK;
-    const int key = is_k ? j / CK : j / CV, ch = is_k ? j % CK : j % CV;
-    const int kidx = key0 + key;
-    const bool valid = kidx <= last;
-    const int kc = valid ? kidx : last;
-    const int page = table[kc / a.page_size];
-    const size_t row = ((size_t)page * a.nkv + kvh) * a.page_size + kc % a.page_size;
-    if (is_k) cp_async16(ks + key * Tile<DK>::PITCH + ch * 16, a.kpages + row * DK + ch * 8, valid);
-    else cp_async16(vs + key * Tile<DV>::PITCH + ch * 16, a.vpages + row * DV + ch * 8, valid);
+  constexpr int CK = DK / 8, CV = DV / 8, TPK = NT / BN;
+  static_assert(NT % BN == 0 && CK % TPK == 0 && CV % TPK == 0, "the chunks of a row divide among its threads");
+  const int key = tid / TPK, part = tid % TPK;
+  const int kidx = key0 + key;
+  const bool valid = kidx <= last;
+  const int kc = valid ? kidx : last;                       // a readable address also for the zero-filled rows
+  const int page = table[kc / a.page_size];
+  const size_t row = ((size_t)page * a.nkv + kvh) * a.page_size + kc % a.page_size;
+  const bf16* kr = a.kpages + row * DK;
+  const bf16* vr = a.vpages + row * DV;
+#pragma unroll
+  for (int i = 0; i < CK / TPK; ++i) {
+    const int ch = part + i * TPK;
+    cp_async16(ks + key * Tile<DK>::PITCH + ch * 16, kr + ch * 8, valid);
+  }
+#pragma unroll
+  for (int i = 0; i < CV / TPK; ++i) {
+    const int ch = part + i * TPK;
+    cp_async16(vs + key * Tile<DV>::PITCH + ch * 16, vr + ch * 8, valid);
   }
 }
 
 // One tile of keys for the warp's 16 rows.  p0/p1: positions of rows g and g+8 (-1: no such row);
-// b1x/b2x: the bias numbers of the rows' heads; [rl, rh]: the keys of the tile that count.
-template <int DK, int DV, int BN>
+// b1x/b2x: the bias numbers of the rows' heads; [rl, rh]: the keys of the tile that count.  FULL: the
+// caller has seen that every key of the tile counts for every row of the warp, so nothing is masked.
+template <int DK, int DV, int BN, bool FULL>
 __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], const unsigned char* ks, const unsigned char* vs,
                                             int key0, int rl, int rh, int p0, int p1, int window, int keep_first, float scale_log2,
                                             float b10, float b20, float b11, float b21, float (&m)[2], float (&l)[2],
@@ -284,17 +294,24 @@ __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], co
 #pragma unroll
     for (int j = 0; j < BN / 8; ++j) mma_bf16(s[j], qf[kk], b[j][0], b[j][1]);
   }
+  // distance of the row's query to the thread's first key of the tile, as a float; the other keys
+  // of the thread lie constants further on
+  const float d0 = (float)(p0 - key0 - 2 * t), d1 = (float)(p1 - key0 - 2 * t);
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int j = 0; j < BN / 8; ++j) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int kidx = key0 + j * 8 + 2 * t + (e & 1);
-      const int p = e < 2 ? p0 : p1;
-      const int dist = p - kidx;
-      const bool ok = kidx >= rl && kidx <= rh && dist >= 0 && (window <= 0 || dist < window || kidx < keep_first);
+      const float fd = (e < 2 ? d0 : d1) - (float)(j * 8 + (e & 1));
       const float b1 = e < 2 ? b10 : b11, b2 = e < 2 ? b20 : b21;
-      s[j][e] = ok ? fmaf(s[j][e], scale_log2, -b1 * __log2f(fmaf(b2, (float)dist, 1.0f))) : -INFINITY;
+      float v = fmaf(s[j][e], scale_log2, -b1 * __log2f(fmaf(b2, fd, 1.0f)));
+      if (!FULL) {
+        const int kidx = key0 + j * 8 + 2 * t + (e & 1);
+        const int dist = (e < 2 ? p0 : p1) - kidx;
+        const bool ok = kidx >= rl && kidx <= rh && dist >= 0 && (window <= 0 || dist < window || kidx < keep_first);
+        v = ok ? v : -INFINITY;
+      }
+      s[j][e] = v;
     }
     mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
     mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
@@ -345,6 +362,12 @@ __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], co
   }
 }
 
+// Whether every key of the tile [key0, key0 + bn) counts for every query of positions p_min .. p_max.
+__device__ __forceinline__ bool tile_is_full(int key0, int bn, int rl, int rh, int p_min, int p_max, int window, int keep_first) {
+  const int last = key0 + bn - 1;
+  return p_min >= 0 && last <= p_min && key0 >= rl && last <= rh && (window <= 0 || p_max - key0 < window || last < keep_first);
+}
+
 template <int DK, int DV>
 __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
   pdl_trigger();
@@ -377,6 +400,9 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
   float o[DV / 8][4];
 #pragma unroll
   for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  // the positions of the warp's 16 rows: the first and the last one (-1 when the warp has rows past the end)
+  const int w_row0 = tile_row0 + warp * 16;
+  const int wp_min = w_row0 + 15 < rows ? start + w_row0 / group : -1, wp_max = start + min(w_row0 + 15, rows - 1) / group;
 
   int key0, rl, rh;
   walk.tile(0, BN, key0, rl, rh);
@@ -396,7 +422,10 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
     }
     __syncthreads();
     walk.tile(i, BN, key0, rl, rh);
-    biased_tile<DK, DV, BN>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+    if (tile_is_full(key0, BN, rl, rh, wp_min, wp_max, a.window, a.keep_first))
+      biased_tile<DK, DV, BN, true>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+    else
+      biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
     __syncthreads();
   }
   const float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
@@ -460,7 +489,7 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
     }
     __syncwarp();
     walk.tile(i, BN, key0, rl, rh);
-    biased_tile<DK, DV, BN>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+    biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
     __syncwarp();
   }
   cp_async_wait<0>();

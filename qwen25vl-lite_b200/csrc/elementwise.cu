@@ -121,17 +121,28 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 template <bool EXACT>
 __device__ __forceinline__ void group_inverse_rms(const float* row_cache, int hidden, int groups, float eps, float* inv,
                                                   float* scratch) {
+  // Each warp takes every (number of warps)-th group: its lanes stride over the group's values, four at
+  // a time where the group's width allows, then a butterfly.  One barrier before (the row is in
+  // shared memory) and one after (every group's figure is there), however many groups there are.
   const int width = hidden / groups;
-  for (int g = 0; g < groups; ++g) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  __syncthreads();
+  for (int g = warp; g < groups; g += nwarps) {
+    const float* part = row_cache + g * width;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      const float v = row_cache[g * width + c];
-      ss = fmaf(v, v, ss);
+    if (width % 4 == 0 && hidden % 4 == 0) {
+      for (int c = lane * 4; c < width; c += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(part + c);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+      }
+    } else {
+      for (int c = lane; c < width; c += 32) ss = fmaf(part[c], part[c], ss);
     }
-    const float total = block_sum(ss, scratch);
-    if (threadIdx.x == 0) inv[g] = EXACT ? 1.0f / sqrtf(total / (float)width + eps) : rsqrtf(total / (float)width + eps);
+    ss = warp_sum(ss);
+    if (lane == 0) inv[g] = EXACT ? 1.0f / sqrtf(ss / (float)width + eps) : rsqrtf(ss / (float)width + eps);
   }
   __syncthreads();
+  (void)scratch;
 }
 
 #define NORM_MAX_GROUPS 64
@@ -166,47 +177,69 @@ __global__ void embed_position_norm_kernel(const T* __restrict__ table, const T*
 // sublayer that is normalised after as well as before); then out[r] = norm_in_groups(x[row]) * w.
 // rows as in add_rmsnorm_kernel: with rows the sum is formed for those rows only and x is left alone.
 // out == nullptr: only the addition.
-template <typename T, bool EXACT>
+template <typename T, bool EXACT, bool VEC>
 __global__ void add_norm_groups_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ dw,
                                        float d_eps, int d_groups, const float* __restrict__ w, float eps, int groups,
                                        T* __restrict__ out, const int* __restrict__ rows, int hidden) {
   pdl_trigger();
   pdl_wait();
-  extern __shared__ __align__(16) float row_cache[];  // 2 * hidden floats + 32 scratch + groups
+  extern __shared__ __align__(16) float row_cache[];  // 2 * hidden floats + 32 scratch + 2 * groups
   float* d_cache = row_cache + hidden;
   float* scratch = d_cache + hidden;
   float* inv = scratch + 32;
+  float* d_inv = inv + NORM_MAX_GROUPS;
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* xr = x + (size_t)row * hidden;
+  constexpr int STEP = VEC ? 4 : 1;
   if (delta) {
     const T* dr = delta + (size_t)row * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) d_cache[c] = to_f32(dr[c]);
-    __syncthreads();
     if (dw) {
-      group_inverse_rms<EXACT>(d_cache, hidden, d_groups, d_eps, inv, scratch);
-      const int dwidth = hidden / d_groups;
-      for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = xr[c] + d_cache[c] * inv[c / dwidth] * dw[c];
-        row_cache[c] = v;
-        if (!rows) xr[c] = v;
+      for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
+        if (VEC) *reinterpret_cast<float4*>(d_cache + c) = load4<T>(dr + c);
+        else d_cache[c] = to_f32(dr[c]);
       }
-    } else {
-      for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = xr[c] + d_cache[c];
+      group_inverse_rms<EXACT>(d_cache, hidden, d_groups, d_eps, d_inv, scratch);
+    }
+    const int dwidth = dw ? hidden / d_groups : hidden;
+    for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
+      if (VEC) {
+        float4 v = *reinterpret_cast<const float4*>(xr + c);
+        if (dw) {
+          const float4 d = *reinterpret_cast<const float4*>(d_cache + c), ww = *reinterpret_cast<const float4*>(dw + c);
+          const float s = d_inv[c / dwidth];
+          v.x += d.x * s * ww.x; v.y += d.y * s * ww.y; v.z += d.z * s * ww.z; v.w += d.w * s * ww.w;
+        } else {
+          const float4 d = load4<T>(dr + c);
+          v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        }
+        *reinterpret_cast<float4*>(row_cache + c) = v;
+        if (!rows) *reinterpret_cast<float4*>(xr + c) = v;
+      } else {
+        const float v = xr[c] + (dw ? d_cache[c] * d_inv[c / dwidth] * dw[c] : to_f32(dr[c]));
         row_cache[c] = v;
         if (!rows) xr[c] = v;
       }
     }
   } else {
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_cache[c] = xr[c];
+    for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
+      if (VEC) *reinterpret_cast<float4*>(row_cache + c) = *reinterpret_cast<const float4*>(xr + c);
+      else row_cache[c] = xr[c];
+    }
   }
   if (!out) return;
-  __syncthreads();
   group_inverse_rms<EXACT>(row_cache, hidden, groups, eps, inv, scratch);
   const int width = hidden / groups;
   T* o = out + (size_t)r * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>(row_cache[c] * inv[c / width] * w[c]);
+  for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
+    if (VEC) {
+      const float4 v = *reinterpret_cast<const float4*>(row_cache + c), ww = *reinterpret_cast<const float4*>(w + c);
+      const float s = inv[c / width];
+      store4<T>(o + c, make_float4(v.x * s * ww.x, v.y * s * ww.y, v.z * s * ww.z, v.w * s * ww.w));
+    } else {
+      o[c] = from_f32<T>(row_cache[c] * inv[c / width] * w[c]);
+    }
+  }
 }
 
 // Gated linear unit with clamped branches: gu is [n, 2*inter], gate in the first half of a row, up
@@ -246,14 +279,22 @@ static int add_norm_groups(float* x, const void* delta, const float* dw, float d
   if (n_out <= 0) return 0;
   if (groups <= 0 || groups > NORM_MAX_GROUPS || hidden % groups) return (int)cudaErrorInvalidValue;
   if (dw && (d_groups <= 0 || d_groups > NORM_MAX_GROUPS || hidden % d_groups)) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)(2 * hidden + 32 + NORM_MAX_GROUPS) * sizeof(float);
+  const size_t smem = (size_t)(2 * hidden + 32 + 2 * NORM_MAX_GROUPS) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
-    const cudaError_t e = cudaFuncSetAttribute(add_norm_groups_kernel<T, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(add_norm_groups_kernel<T, EXACT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(add_norm_groups_kernel<T, EXACT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  launch(add_norm_groups_kernel<T, EXACT>, dim3(n_out), dim3(hidden >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, x,
-         (const T*)delta, dw, d_eps, d_groups, w, eps, groups, (T*)out, rows, hidden);
+  // four values at a time when every group (of the stream's norm and of the update's) is a multiple of
+  // four wide and every row starts on a 16-byte boundary
+  const bool vec = hidden % 4 == 0 && (hidden / groups) % 4 == 0 && (!dw || (hidden / d_groups) % 4 == 0) &&
+                   !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)dw | (uintptr_t)w | (uintptr_t)out) & 15);
+  const dim3 block(hidden >= 1024 ? 256 : 128);
+  if (vec) launch(add_norm_groups_kernel<T, EXACT, true>, dim3(n_out), block, smem, (cudaStream_t)stream, x, (const T*)delta, dw, d_eps,
+                  d_groups, w, eps, groups, (T*)out, rows, hidden);
+  else launch(add_norm_groups_kernel<T, EXACT, false>, dim3(n_out), block, smem, (cudaStream_t)stream, x, (const T*)delta, dw, d_eps,
+              d_groups, w, eps, groups, (T*)out, rows, hidden);
   return launch_status();
 }
 

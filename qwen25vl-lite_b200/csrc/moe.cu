@@ -22,38 +22,53 @@
 #define MOE_MAX_EXPERTS 256
 #define MOE_MAX_TOP 16
 
-// One warp per token: router logits in float (the lanes stride over the channels, then a butterfly:
-// a fixed order), the choice of the `top` largest (ties to the lower index), the shared expert's gate.
+// One block of 4 warps per token: the token's row is widened to float in shared memory once; each
+// warp takes every fourth expert (and the last warp's turn the shared expert's gate) and forms
+// its logit with the lanes striding over the channels four at a time, then a butterfly: an order
+// that depends on the sizes alone.  Warp 0 then picks the `top` largest (ties to the lower index).
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ shared_gate,
-                                 int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ sg,
-                                 int* __restrict__ counts, int n_tokens, int hidden, int experts, int top) {
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ shared_gate,
+                 int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ sg,
+                 int* __restrict__ counts, int n_tokens, int hidden, int experts, int top) {
   pdl_trigger();
   pdl_wait();
-  __shared__ float zs[4][MOE_MAX_EXPERTS];
+  extern __shared__ __align__(16) float route_smem[];       // hidden floats, then MOE_MAX_EXPERTS + 1 logits
+  float* xs = route_smem;
+  float* zs = route_smem + ((hidden + 3) & ~3);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * 4 + warp;
-  if (n >= n_tokens) return;
+  const int n = blockIdx.x;
   const T* row = h + (size_t)n * hidden;
-  for (int e = 0; e < experts; ++e) {
-    const float* w = router + (size_t)e * hidden;
+  for (int c = threadIdx.x; c < hidden; c += 128) xs[c] = to_f32(row[c]);
+  __syncthreads();
+  const int n_dots = experts + (shared_gate ? 1 : 0);
+  const bool vec = hidden % 4 == 0 && !(((uintptr_t)router | (uintptr_t)shared_gate) & 15);
+  for (int e = warp; e < n_dots; e += 4) {
+    const float* w = e < experts ? router + (size_t)e * hidden : shared_gate;
     float acc = 0.f;
-    for (int c = lane; c < hidden; c += 32) acc = fmaf(w[c], to_f32(row[c]), acc);
+    if (vec) {
+#pragma unroll 4
+      for (int c = lane * 4; c < hidden; c += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + c), xv = *reinterpret_cast<const float4*>(xs + c);
+        acc = fmaf(wv.x, xv.x, acc);
+        acc = fmaf(wv.y, xv.y, acc);
+        acc = fmaf(wv.z, xv.z, acc);
+        acc = fmaf(wv.w, xv.w, acc);
+      }
+    } else {
+      for (int c = lane; c < hidden; c += 32) acc = fmaf(w[c], xs[c], acc);
+    }
     acc = warp_sum(acc);
-    if (lane == 0) zs[warp][e] = acc;
+    if (lane == 0) zs[e] = acc;
   }
-  if (shared_gate) {
-    float acc = 0.f;
-    for (int c = lane; c < hidden; c += 32) acc = fmaf(shared_gate[c], to_f32(row[c]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) sg[n] = 1.0f / (1.0f + expf(-acc));
-  }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
+  if (shared_gate && lane == 0) sg[n] = 1.0f / (1.0f + expf(-zs[experts]));
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
     for (int e = lane; e < experts; e += 32) {
-      const float z = zs[warp][e];
+      const float z = zs[e];
       if (z > best) { best = z; arg = e; }
     }
 #pragma unroll
@@ -65,7 +80,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     if (lane == 0) {
       topk_idx[(size_t)n * top + k] = arg;
       topk_w[(size_t)n * top + k] = 1.0f / (1.0f + expf(-best));
-      zs[warp][arg] = -INFINITY;
+      zs[arg] = -INFINITY;
       atomicAdd(&counts[arg], 1);
     }
     __syncwarp();
@@ -201,39 +216,76 @@ moe_grouped_fma_kernel(const T* __restrict__ A, const T* __restrict__ W0, const 
   }
 }
 
-// The grouped products on the tensor cores (bfloat16, mma.sync m16n8k16, float accumulators): a CTA
-// of 4 warps takes a tile of BM rows x 64 columns of one expert; with BM = 64 a warp holds 16 rows and
-// all 64 columns, with BM = 16 all rows and 16 columns.  K is walked in steps of 32: the weights'
-// rows by 16-byte cp.async, the rows of A by plain loads (gate and up: the token's row times its
-// weight, rounded to bfloat16), one stage: several CTAs share an SM and hide each other's loads.
-// Every element's sum runs over K in the same order whatever tile the row is in.
-template <bool GATE_UP, int BM>
-__global__ void __launch_bounds__(128)
-moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, const bf16* __restrict__ W1, void* __restrict__ out_,
-                       const int* __restrict__ plan, const int* __restrict__ row_pair, const float* __restrict__ topk_w,
-                       int experts, int top, int N, int K, float limit, float alpha) {
+// The rows of the sorted pairs as the tensor-core product reads them: sorted[row, :] = weight of
+// the pair * h[token of the pair, :], rounded to bfloat16.  One block per row; empty rows are left
+// as they are (their products are never stored).
+__global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restrict__ row_pair, const float* __restrict__ topk_w,
+                                  bf16* __restrict__ sorted, int top, int K) {
   pdl_trigger();
   pdl_wait();
-  constexpr int BN = 64, BK = 32, P = BK * 2 + 16;            // pitch in bytes: an odd number of 16-byte chunks
+  const int pair = row_pair[blockIdx.x];
+  if (pair < 0) return;
+  const float w = topk_w[pair];
+  const bf16* src = h + (size_t)(pair / top) * K;
+  bf16* dst = sorted + (size_t)blockIdx.x * K;
+  for (int c = threadIdx.x * 8; c < K; c += blockDim.x * 8) {
+    uint4 v = *reinterpret_cast<const uint4*>(src + c);
+    unsigned* u = reinterpret_cast<unsigned*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&u[i]);
+      u[i] = pack_bf16(__low2float(x) * w, __high2float(x) * w);
+    }
+    *reinterpret_cast<uint4*>(dst + c) = v;
+  }
+}
+
+// The grouped products on the tensor cores (bfloat16, mma.sync m16n8k16, float accumulators): a CTA
+// of 4 warps takes a tile of BM rows x 64 columns of one expert; with BM = 64 a warp holds 16 rows and
+// all 64 columns, with BM = 16 all rows and 16 columns.  A is [rows, K], the rows in the sorted
+// order.  K is walked in steps of 64 through a ring of STAGES stages filled by 16-byte cp.async (the
+// rows of A and of the weights alike), so that a CTA always has several stages of weights in
+// flight: a step of few rows is a stream of the experts' weights.  Every element's sum runs over
+// K in the same order whatever tile the row is in.
+template <bool GATE_UP, int BM, int STAGES>
+__global__ void __launch_bounds__(128)
+moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, const bf16* __restrict__ W1, void* __restrict__ out_,
+                       const int* __restrict__ plan, const int* __restrict__ row_pair, int experts, int N, int K, float limit,
+                       float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int BN = 64, BK = 64, P = BK * 2 + 16;            // pitch in bytes: an odd number of 16-byte chunks
   constexpr int WN = BM == 64 ? 64 : 16;                      // columns a warp holds
+  constexpr int A_BYTES = BM * P, W_BYTES = BN * P, STAGE = A_BYTES + (GATE_UP ? 2 : 1) * W_BYTES;
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
   const int e = plan[2 + experts + tile];
-  __shared__ __align__(16) unsigned char As[BM * P];
-  __shared__ __align__(16) unsigned char Ws0[BN * P];
-  __shared__ __align__(16) unsigned char Ws1[GATE_UP ? BN * P : 16];
+  extern __shared__ __align__(16) unsigned char ring[];
   __shared__ int src_row[BM];
-  __shared__ float src_w[BM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int m0 = tile * BM, n0 = blockIdx.x * BN;
-  for (int r = threadIdx.x; r < BM; r += 128) {
-    const int pair = row_pair[m0 + r];
-    src_row[r] = pair < 0 ? -1 : (GATE_UP ? pair / top : m0 + r);
-    src_w[r] = (GATE_UP && pair >= 0) ? topk_w[pair] : 1.f;
-  }
-  __syncthreads();
+  for (int r = threadIdx.x; r < BM; r += 128) src_row[r] = row_pair[m0 + r];
   const bf16* w0 = W0 + (size_t)e * N * K;
   const bf16* w1 = GATE_UP ? W1 + (size_t)e * N * K : nullptr;
+  const bf16* a0 = A + (size_t)m0 * K;
+  const int nk = (K + BK - 1) / BK;
+  auto load = [&](int kt) {
+    unsigned char* st = ring + (kt % STAGES) * STAGE;
+    const int k0 = kt * BK;
+    for (int x = threadIdx.x; x < (BM + BN) * (BK / 8); x += 128) {
+      const int r = x / (BK / 8), ch = x % (BK / 8);
+      const int gk = k0 + ch * 8;
+      if (r < BM) {
+        cp_async16(st + r * P + ch * 16, a0 + (gk < K ? (size_t)r * K + gk : 0), gk < K);
+      } else {
+        const int gn = n0 + r - BM;
+        const bool ok = gn < N && gk < K;
+        const size_t off = ok ? (size_t)gn * K + gk : 0;
+        cp_async16(st + A_BYTES + (r - BM) * P + ch * 16, w0 + off, ok);
+        if (GATE_UP) cp_async16(st + A_BYTES + W_BYTES + (r - BM) * P + ch * 16, w1 + off, ok);
+      }
+    }
+  };
   const int row_base = BM == 64 ? warp * 16 : 0, col_base = BM == 64 ? 0 : warp * 16;
   float acc0[WN / 8][4], acc1[GATE_UP ? WN / 8 : 1][4];
 #pragma unroll
@@ -242,40 +294,23 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
 #pragma unroll
     for (int j = 0; j < WN / 8; ++j) acc1[j][0] = acc1[j][1] = acc1[j][2] = acc1[j][3] = 0.f;
   }
-  for (int k0 = 0; k0 < K; k0 += BK) {
-    for (int x = threadIdx.x; x < BN * (BK / 8); x += 128) {
-      const int r = x / (BK / 8), ch = x % (BK / 8);
-      const int gn = n0 + r, gk = k0 + ch * 8;
-      const bool ok = gn < N && gk < K;
-      const size_t off = ok ? (size_t)gn * K + gk : 0;
-      cp_async16(Ws0 + r * P + ch * 16, w0 + off, ok);
-      if (GATE_UP) cp_async16(Ws1 + r * P + ch * 16, w1 + off, ok);
-    }
-    cp_async_commit();
-    for (int x = threadIdx.x; x < BM * (BK / 8); x += 128) {
-      const int r = x / (BK / 8), ch = x % (BK / 8);
-      const int gk = k0 + ch * 8, src = src_row[r];
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (src >= 0 && gk < K) {
-        v = *reinterpret_cast<const uint4*>(A + (size_t)src * K + gk);
-        if (GATE_UP) {
-          const float w = src_w[r];
-          unsigned* u = reinterpret_cast<unsigned*>(&v);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&u[i]);
-            u[i] = pack_bf16(__low2float(b) * w, __high2float(b) * w);
-          }
-        }
-      }
-      *reinterpret_cast<uint4*>(As + r * P + ch * 16) = v;
-    }
-    cp_async_wait<0>();
-    __syncthreads();
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < nk) load(s);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < nk; ++kt) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();                          // tile kt has landed, and everybody is done with tile kt - 1
+    if (kt + STAGES - 1 < nk) load(kt + STAGES - 1);
+    cp_async_commit();
+    const unsigned char* st = ring + (kt % STAGES) * STAGE;
+    const unsigned char* Ws0 = st + A_BYTES;
+    const unsigned char* Ws1 = Ws0 + W_BYTES;
 #pragma unroll
     for (int kk = 0; kk < BK / 16; ++kk) {
       unsigned a[4];
-      ldmatrix_x4(a, As + (row_base + (lane & 15)) * P + (kk * 16 + 8 * (lane >> 4)) * 2);
+      ldmatrix_x4(a, st + (row_base + (lane & 15)) * P + (kk * 16 + 8 * (lane >> 4)) * 2);
 #pragma unroll
       for (int j = 0; j < WN / 8; ++j) {
         unsigned b[2];
@@ -287,26 +322,28 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
         }
       }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int j = 0; j < WN / 8; ++j) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int r = row_base + g + 8 * half;
       if (src_row[r] < 0) continue;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int gn = n0 + col_base + j * 8 + 2 * t + c;
-        if (gn >= N) continue;
-        const float v0 = acc0[j][2 * half + c];
-        if (GATE_UP) {
-          const float gt = fminf(v0, limit);
-          const float up = fminf(fmaxf(acc1[j][2 * half + c], -limit), limit);
-          reinterpret_cast<bf16*>(out_)[(size_t)(m0 + r) * N + gn] = __float2bfloat16_rn(gt / (1.0f + expf(-alpha * gt)) * (up + 1.0f));
-        } else {
-          reinterpret_cast<float*>(out_)[(size_t)(m0 + r) * N + gn] = v0;
-        }
+      const int gn = n0 + col_base + j * 8 + 2 * t;
+      if (gn >= N) continue;
+      const float v0 = acc0[j][2 * half], v1 = acc0[j][2 * half + 1];
+      if (GATE_UP) {
+        const float g0 = fminf(v0, limit), g1 = fminf(v1, limit);
+        const float u0 = fminf(fmaxf(acc1[j][2 * half], -limit), limit), u1 = fminf(fmaxf(acc1[j][2 * half + 1], -limit), limit);
+        const float y0 = g0 / (1.0f + expf(-alpha * g0)) * (u0 + 1.0f), y1 = g1 / (1.0f + expf(-alpha * g1)) * (u1 + 1.0f);
+        bf16* o = reinterpret_cast<bf16*>(out_) + (size_t)(m0 + r) * N + gn;
+        if (gn + 1 < N && N % 2 == 0) *reinterpret_cast<unsigned*>(o) = pack_bf16(y0, y1);
+        else { o[0] = __float2bfloat16_rn(y0); if (gn + 1 < N) o[1] = __float2bfloat16_rn(y1); }
+      } else {
+        float* o = reinterpret_cast<float*>(out_) + (size_t)(m0 + r) * N + gn;
+        o[0] = v0;
+        if (gn + 1 < N) o[1] = v1;
       }
     }
   }
@@ -340,7 +377,13 @@ static int moe_route(const void* h, const float* router, const float* shared_gat
                      int* counts, int n_tokens, int hidden, int experts, int top, void* stream) {
   if (n_tokens <= 0) return 0;
   if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts || top > MOE_MAX_TOP) return (int)cudaErrorInvalidValue;
-  launch(moe_route_kernel<T>, dim3((n_tokens + 3) / 4), dim3(128), 0, (cudaStream_t)stream, (const T*)h, router, shared_gate, topk_idx,
+  const size_t smem = (size_t)(((hidden + 3) & ~3) + MOE_MAX_EXPERTS + 4) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(moe_route_kernel<T>, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, (const T*)h, router, shared_gate, topk_idx,
          topk_w, sg, counts, n_tokens, hidden, experts, top);
   return launch_status();
 }
@@ -365,21 +408,30 @@ Q25_EXPORT int q25_moe_sort(const int* topk_idx, const int* counts, int* cursor,
   return launch_status();
 }
 
+template <bool GATE_UP, int BM, int STAGES>
+static int moe_grouped_mma_shape(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
+                                 int tiles, int experts, int N, int K, float limit, float alpha, cudaStream_t s) {
+  constexpr int SMEM = STAGES * (BM + (GATE_UP ? 128 : 64)) * (64 * 2 + 16);
+  const cudaError_t e = cudaFuncSetAttribute(moe_grouped_mma_kernel<GATE_UP, BM, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) return (int)e;
+  launch(moe_grouped_mma_kernel<GATE_UP, BM, STAGES>, dim3((N + 63) / 64, tiles), dim3(128), SMEM, s, (const bf16*)A, (const bf16*)W0,
+         (const bf16*)W1, out, plan, row_pair, experts, N, K, limit, alpha);
+  return launch_status();
+}
+
+// A: the rows in the sorted order, [rows, K] bfloat16.
 template <bool GATE_UP>
 static int moe_grouped_mma(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
-                           const float* topk_w, int n_pairs, int experts, int top, int N, int K, float limit, float alpha, int tile,
-                           void* stream) {
+                           int n_pairs, int experts, int N, int K, float limit, float alpha, int tile, void* stream) {
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
-  if (tile == 16) {
-    launch(moe_grouped_mma_kernel<GATE_UP, 16>, dim3((N + 63) / 64, tiles), dim3(128), 0, (cudaStream_t)stream, (const bf16*)A,
-           (const bf16*)W0, (const bf16*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
-  } else if (tile == 64) {
-    launch(moe_grouped_mma_kernel<GATE_UP, 64>, dim3((N + 63) / 64, tiles), dim3(128), 0, (cudaStream_t)stream, (const bf16*)A,
-           (const bf16*)W0, (const bf16*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
-  } else {
-    return (int)cudaErrorInvalidValue;
-  }
-  return launch_status();
+  cudaStream_t s = (cudaStream_t)stream;
+  if (tile == 16) return moe_grouped_mma_shape<GATE_UP, 16, 4>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
+  if (tile == 64) return moe_grouped_mma_shape<GATE_UP, 64, 3>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
+  return (int)cudaErrorInvalidValue;
+}
+
+static bool moe_mma_takes(const void* A, const void* W0, const void* W1, const void* extra, int K) {
+  return K % 8 == 0 && !(((uintptr_t)A | (uintptr_t)W0 | (uintptr_t)W1 | (uintptr_t)extra) & 15);
 }
 
 template <typename T, bool GATE_UP>
@@ -387,9 +439,6 @@ static int moe_grouped_fma(const void* A, const void* W0, const void* W1, void* 
                            const float* topk_w, int n_pairs, int experts, int top, int N, int K, float limit, float alpha, int tile,
                            void* stream) {
   if (n_pairs <= 0) return 0;
-  // bfloat16 operands whose rows start on 16-byte boundaries go to the tensor cores
-  if (sizeof(T) == 2 && K % 8 == 0 && !(((uintptr_t)A | (uintptr_t)W0 | (uintptr_t)W1) & 15))
-    return moe_grouped_mma<GATE_UP>(A, W0, W1, out, plan, row_pair, topk_w, n_pairs, experts, top, N, K, limit, alpha, tile, stream);
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
   if (tile == 16) {
     launch(moe_grouped_fma_kernel<T, GATE_UP, 16, 64, 16, 1, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
@@ -403,14 +452,22 @@ static int moe_grouped_fma(const void* A, const void* W0, const void* W1, void* 
   return launch_status();
 }
 
+// sorted: [max rows, hidden] of scratch in the activation dtype for the rows in the sorted order
+// (bfloat16: the tensor-core product reads them; nullptr or float: the product gathers by itself).
 Q25_EXPORT int q25_moe_gate_up_f32(const void* h, const void* wg, const void* wu, void* act, const int* plan, const int* row_pair,
                                    const float* topk_w, int n_pairs, int experts, int top, int ff, int hidden, float limit,
-                                   float alpha, int tile, void* s) {
+                                   float alpha, int tile, void* sorted, void* s) {
   return moe_grouped_fma<float, true>(h, wg, wu, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden, limit, alpha, tile, s);
 }
 Q25_EXPORT int q25_moe_gate_up_bf16(const void* h, const void* wg, const void* wu, void* act, const int* plan, const int* row_pair,
                                     const float* topk_w, int n_pairs, int experts, int top, int ff, int hidden, float limit,
-                                    float alpha, int tile, void* s) {
+                                    float alpha, int tile, void* sorted, void* s) {
+  if (n_pairs <= 0) return 0;
+  if (sorted && moe_mma_takes(h, wg, wu, sorted, hidden)) {
+    launch(moe_gather_kernel, dim3(q25_moe_max_rows(n_pairs, experts, tile)), dim3(128), 0, (cudaStream_t)s, (const bf16*)h, row_pair, topk_w,
+           (bf16*)sorted, top, hidden);
+    return moe_grouped_mma<true>(sorted, wg, wu, act, plan, row_pair, n_pairs, experts, ff, hidden, limit, alpha, tile, s);
+  }
   return moe_grouped_fma<bf16, true>(h, wg, wu, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden, limit, alpha, tile, s);
 }
 Q25_EXPORT int q25_moe_down_f32(const void* act, const void* wd, void* y, const int* plan, const int* row_pair, int n_pairs,
@@ -419,6 +476,9 @@ Q25_EXPORT int q25_moe_down_f32(const void* act, const void* wd, void* y, const 
 }
 Q25_EXPORT int q25_moe_down_bf16(const void* act, const void* wd, void* y, const int* plan, const int* row_pair, int n_pairs,
                                  int experts, int top, int hidden, int ff, int tile, void* s) {
+  if (n_pairs <= 0) return 0;
+  if (moe_mma_takes(act, wd, nullptr, nullptr, ff))
+    return moe_grouped_mma<false>(act, wd, nullptr, y, plan, row_pair, n_pairs, experts, hidden, ff, 0.f, 0.f, tile, s);
   return moe_grouped_fma<bf16, false>(act, wd, nullptr, y, plan, row_pair, nullptr, n_pairs, experts, top, hidden, ff, 0.f, 0.f, tile, s);
 }
 

@@ -15,8 +15,9 @@
 // Per-request state [slots, taps, W] float: row 0 is S, rows 1 .. taps-1 are the last taps-1 inputs
 // xin of the request, oldest first (zeros at admission, which are the zeros before the start).
 //
-// Three kernels: the convolution; the two gates of all blocks as one batched FMA product with the
-// decay and the input term formed in its epilogue; the scan, which also moves the state on.
+// The kernels: the convolution; the two gates of all blocks as one batched FMA product with the
+// decay and the input term formed in its epilogue; the scan in chunks over time, which also moves
+// the state on.
 #include "common.cuh"
 
 #define RG_MAX_TAPS 16
@@ -126,25 +127,69 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// One thread per (entry, channel): S runs over the entry's tokens from the request's state; then the
-// state moves on: S, and the last taps-1 inputs of (old inputs ++ this entry's inputs).
-template <typename T>
-__global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ bx, const T* __restrict__ yx, int ld,
-                                  int y_off, int x_off, float* __restrict__ state, const int* __restrict__ cu_q,
-                                  const int* __restrict__ slot_ids, T* __restrict__ out, int n_seqs, int width, int taps) {
+// The scan S_t = a_t S_(t-1) + bx_t over an entry's tokens, cut into chunks of RG_CHUNK tokens so
+// that long prompts run in parallel over time as well as over channels.
+//   rglru_chunk_kernel: one thread per (entry, chunk, channel) folds its chunk into (A, B) with
+//     S_end = A S_start + B (A the product of the decays, B the chunk's own sum from zero); the
+//     thread of chunk 0 also copies the request's S aside, so that the next kernel never reads the
+//     place it writes.
+//   rglru_scan_kernel: one thread per (entry, chunk, channel) folds the summaries of the chunks
+//     before its own onto the request's S (a short chain of FMAs over values that all chunks of
+//     the entry read, so they stay in cache), then runs its chunk and writes out = S * gelu_tanh(y).
+//     The thread of the last chunk moves the state on: S, and the last taps-1 inputs of (old
+//     inputs ++ this entry's inputs).
+// A step whose entries all have up to RG_CHUNK tokens (every decode step) runs the second kernel
+// alone: one chunk per entry, S read from the state itself.
+// sums: [n_seqs, max_chunks, 2, width] (A, B), then [n_seqs, width] (the requests' S before the step).
+#define RG_CHUNK 32
+
+__global__ void rglru_chunk_kernel(const float* __restrict__ a, const float* __restrict__ bx, const float* __restrict__ state,
+                                   const int* __restrict__ cu_q, const int* __restrict__ slot_ids, float* __restrict__ sums,
+                                   int n_seqs, int width, int taps, int max_chunks) {
   pdl_trigger();
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int seq = blockIdx.y;
-  if (c >= width || seq >= n_seqs) return;
+  const int seq = blockIdx.y, chunk = blockIdx.z;
   const int first = cu_q[seq], n = cu_q[seq + 1] - first;
+  if (c >= width || chunk * RG_CHUNK >= n) return;
+  if (chunk == 0) sums[(size_t)n_seqs * max_chunks * 2 * width + (size_t)seq * width + c] = state[(size_t)slot_ids[seq] * taps * width + c];
+  const int t0 = chunk * RG_CHUNK, t1 = min(n, t0 + RG_CHUNK);
+  float A = 1.f, B = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const size_t at = (size_t)(first + t) * width + c;
+    const float av = a[at];
+    A *= av;
+    B = fmaf(av, B, bx[at]);
+  }
+  const size_t to = ((size_t)seq * max_chunks + chunk) * 2 * width + c;
+  sums[to] = A;
+  sums[to + width] = B;
+}
+
+template <typename T>
+__global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ bx, const T* __restrict__ yx, int ld,
+                                  int y_off, int x_off, float* __restrict__ state, const int* __restrict__ cu_q,
+                                  const int* __restrict__ slot_ids, T* __restrict__ out, const float* __restrict__ sums,
+                                  int n_seqs, int width, int taps, int max_chunks) {
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int seq = blockIdx.y, chunk = blockIdx.z;
+  const int first = cu_q[seq], n = cu_q[seq + 1] - first;
+  if (c >= width || chunk * RG_CHUNK >= n) return;
   float* st = state + (size_t)slot_ids[seq] * taps * width + c;
-  float S = st[0];
-  for (int t = 0; t < n; ++t) {
+  float S = sums ? sums[(size_t)n_seqs * max_chunks * 2 * width + (size_t)seq * width + c] : st[0];
+  for (int j = 0; j < chunk; ++j) {
+    const size_t at = ((size_t)seq * max_chunks + j) * 2 * width + c;
+    S = fmaf(sums[at], S, sums[at + width]);
+  }
+  const int t0 = chunk * RG_CHUNK, t1 = min(n, t0 + RG_CHUNK);
+  for (int t = t0; t < t1; ++t) {
     const size_t at = (size_t)(first + t) * width + c;
     S = fmaf(a[at], S, bx[at]);
     out[at] = from_f32<T>(S * gelu_tanh_f(to_f32(yx[(size_t)(first + t) * ld + y_off + c])));
   }
+  if (t1 < n) return;                          // the last chunk's thread moves the state on; nobody else reads it here
   st[0] = S;
   float keep[RG_MAX_TAPS];
 #pragma unroll
@@ -174,13 +219,25 @@ static int rglru_conv(const void* yx, int ld, int x_off, const float* conv_w, co
   return launch_status();
 }
 
+// Floats of scratch memory the scan needs for a step whose longest entry has max_q_len tokens (0: none).
+Q25_EXPORT long long q25_rglru_scan_scratch_floats(int n_seqs, int max_q_len, int width) {
+  const int max_chunks = (max_q_len + RG_CHUNK - 1) / RG_CHUNK;
+  return max_chunks <= 1 ? 0 : (long long)n_seqs * width * (2 * max_chunks + 1);
+}
+
 template <typename T>
 static int rglru_scan(const float* a, const float* bx, const void* yx, int ld, int y_off, int x_off, float* state, const int* cu_q,
-                      const int* slot_ids, void* out, int n_seqs, int width, int taps, void* stream) {
+                      const int* slot_ids, void* out, int n_seqs, int max_q_len, float* sums, int width, int taps, void* stream) {
   if (n_seqs <= 0) return 0;
-  if (taps < 1 || taps > RG_MAX_TAPS) return (int)cudaErrorInvalidValue;
-  launch(rglru_scan_kernel<T>, dim3((width + 127) / 128, n_seqs), dim3(128), 0, (cudaStream_t)stream, a, bx, (const T*)yx, ld, y_off,
-         x_off, state, cu_q, slot_ids, (T*)out, n_seqs, width, taps);
+  if (taps < 1 || taps > RG_MAX_TAPS || max_q_len < 1) return (int)cudaErrorInvalidValue;
+  const int max_chunks = (max_q_len + RG_CHUNK - 1) / RG_CHUNK;
+  if (max_chunks > 65535 || (max_chunks > 1 && !sums)) return (int)cudaErrorInvalidValue;
+  const dim3 grid((width + 127) / 128, n_seqs, max_chunks);
+  if (max_chunks > 1)
+    launch(rglru_chunk_kernel, grid, dim3(128), 0, (cudaStream_t)stream, a, bx, (const float*)state, cu_q, slot_ids, sums, n_seqs, width,
+           taps, max_chunks);
+  launch(rglru_scan_kernel<T>, grid, dim3(128), 0, (cudaStream_t)stream, a, bx, (const T*)yx, ld, y_off, x_off, state, cu_q, slot_ids,
+         (T*)out, (const float*)(max_chunks > 1 ? sums : nullptr), n_seqs, width, taps, max_chunks);
   return launch_status();
 }
 
@@ -208,10 +265,10 @@ Q25_EXPORT int q25_rglru_gates(const float* u, const float* ra, const float* ra_
   return launch_status();
 }
 Q25_EXPORT int q25_rglru_scan_f32(const float* a, const float* bx, const void* yx, int ld, int yo, int xo, float* st, const int* cu,
-                                  const int* sl, void* out, int n_seqs, int w, int taps, void* s) {
-  return rglru_scan<float>(a, bx, yx, ld, yo, xo, st, cu, sl, out, n_seqs, w, taps, s);
+                                  const int* sl, void* out, int n_seqs, int max_q_len, float* sums, int w, int taps, void* s) {
+  return rglru_scan<float>(a, bx, yx, ld, yo, xo, st, cu, sl, out, n_seqs, max_q_len, sums, w, taps, s);
 }
 Q25_EXPORT int q25_rglru_scan_bf16(const float* a, const float* bx, const void* yx, int ld, int yo, int xo, float* st, const int* cu,
-                                   const int* sl, void* out, int n_seqs, int w, int taps, void* s) {
-  return rglru_scan<bf16>(a, bx, yx, ld, yo, xo, st, cu, sl, out, n_seqs, w, taps, s);
+                                   const int* sl, void* out, int n_seqs, int max_q_len, float* sums, int w, int taps, void* s) {
+  return rglru_scan<bf16>(a, bx, yx, ld, yo, xo, st, cu, sl, out, n_seqs, max_q_len, sums, w, taps, s);
 }

@@ -30,11 +30,11 @@ _SIGNATURES = {
     "q25_add_norm_groups": [_P, _P, _P, _F, _I, _P, _F, _I, _P, _P, _I, _I, _P],
     "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _P],
     "q25_rglru_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
-    "q25_rglru_scan": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_rglru_scan": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P],
     "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "q25_kv_store_mix": [_P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "q25_moe_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
@@ -702,15 +702,22 @@ def rglru_gates(u: torch.Tensor, ra: torch.Tensor, ra_b: torch.Tensor, ri: torch
 
 
 def rglru_scan(a: torch.Tensor, bx: torch.Tensor, yx: torch.Tensor, y_off: int, x_off: int, state: torch.Tensor,
-               cu_q: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor, n_seqs: int) -> None:
+               cu_q: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q_len: int) -> None:
     """S = a S + bx over every entry's tokens from the request's state (row 0 of ``state``), out = S *
-    gelu_tanh(yx[:, y_off + c]); the state (S and the last taps - 1 inputs) moves on."""
+    gelu_tanh(yx[:, y_off + c]); the state (S and the last taps - 1 inputs) moves on.  ``max_q_len``:
+    the step's longest entry; entries beyond a chunk of tokens are scanned in chunks, in parallel."""
     width = out.shape[1]
     taps = state.shape[1]
     _dev(out, yx.dtype, "rglru_scan out")
+    need = _fn("q25_rglru_scan_scratch_floats", [_I, _I, _I])
+    need.restype = ctypes.c_longlong
+    floats = need(int(n_seqs), int(max_q_len), width)
+    sums = torch.empty(floats, dtype=torch.float32, device=out.device) if floats else None
     _check(_typed("q25_rglru_scan", yx.dtype)(a.data_ptr(), bx.data_ptr(), yx.data_ptr(), yx.stride(0), int(y_off), int(x_off),
                                               state.data_ptr(), cu_q.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), int(n_seqs),
-                                              width, taps, _stream()), "rglru_scan")
+                                              int(max_q_len), _ptr(sums), width, taps, _stream()), "rglru_scan")
+    if floats:
+        count_replayed(1)                      # the chunk summaries' kernel, launched by the same call
 
 
 # ---- attention with a distance bias, kept first tokens and values of their own size ---------------------
@@ -807,11 +814,17 @@ def moe_sort(topk_idx: torch.Tensor, counts: torch.Tensor, cursor: torch.Tensor,
 
 def moe_gate_up(h: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, act: torch.Tensor, plan: torch.Tensor,
                 row_pair: torch.Tensor, topk_w: torch.Tensor, top: int, limit: float, alpha: float, tile: int) -> None:
+    """act[row] = glu(expert of the row's tile applied to weight * h[token of the row]) for the sorted rows."""
     experts, ff, hidden = w_gate.shape
+    _dev(h, act.dtype, "moe_gate_up input")
     _dev(w_gate, h.dtype, "moe_gate_up gate"); _dev(w_up, h.dtype, "moe_gate_up up"); _dev(act, h.dtype, "moe_gate_up act")
+    # bfloat16: the rows are first written out in the sorted order, weighted, for the tensor-core product
+    sorted_rows = torch.empty((act.shape[0], hidden), dtype=h.dtype, device=h.device) if h.dtype == torch.bfloat16 else None
     _check(_typed("q25_moe_gate_up", h.dtype)(h.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), act.data_ptr(), plan.data_ptr(),
                                               row_pair.data_ptr(), topk_w.data_ptr(), topk_w.numel(), experts, int(top), ff, hidden,
-                                              float(limit), float(alpha), int(tile), _stream()), "moe_gate_up")
+                                              float(limit), float(alpha), int(tile), _ptr(sorted_rows), _stream()), "moe_gate_up")
+    if sorted_rows is not None:
+        count_replayed(1)
 
 
 def moe_down(act: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor, plan: torch.Tensor, row_pair: torch.Tensor, n_pairs: int,

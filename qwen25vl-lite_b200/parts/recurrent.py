@@ -61,11 +61,10 @@ class RGLRU(Mixer):
     def forward(self, ctx, h, stop):
         n, w = h.shape[0], self.width
         yx = self.in_proj(h)                                    # [N, 2 width]: the y branch, then the convolution's input
-        kernels.chain_flush()
         u = torch.empty((n, w), dtype=torch.float32, device=h.device)
         kernels.rglru_conv(yx, w, self.conv_w, self.conv_b, stop.state, ctx.token_seq, ctx.cu_q, ctx.slot_ids, u)
         a, bx = torch.empty_like(u), torch.empty_like(u)
         kernels.rglru_gates(u, self.ra, self.ra_b, self.ri, self.ri_b, self.lam, self.gain, a, bx)
         out = torch.empty((n, w), dtype=ctx.dtype, device=h.device)
-        kernels.rglru_scan(a, bx, yx, 0, w, stop.state, ctx.cu_q, ctx.slot_ids, out, ctx.n_seqs)
+        kernels.rglru_scan(a, bx, yx, 0, w, stop.state, ctx.cu_q, ctx.slot_ids, out, ctx.n_seqs, ctx.max_q_len)
         return self.out_proj(out)

@@ -23,8 +23,8 @@ F32_TOLERANCE = 2e-5
 # (BF16_SHARE of them within BF16_TOLERANCE), and to the engine's own logits for each request alone
 # and whole on nearly all: what the schedule, the pages and the slots could change.  The 32-bit
 # runs, where no choice is close on this scale, are held to the plain implementation everywhere.
-BF16_TOLERANCE = {"R1": 0.03, "R2": 0.03, "R3": 0.05}
-BF16_SHARE = 0.85
+BF16_TOLERANCE = {"R1": 0.03, "R2": 0.03, "R3": 0.08}
+BF16_SHARE = 0.80
 BF16_SCHEDULE_TOLERANCE, BF16_SCHEDULE_SHARE = 0.02, 0.90
 
 
