@@ -241,13 +241,15 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restr
 }
 
 // The grouped products on the tensor cores (bfloat16, mma.sync m16n8k16, float accumulators): a CTA
-// of 4 warps takes a tile of BM rows x 64 columns of one expert; with BM = 64 a warp holds 16 rows and
-// all 64 columns, with BM = 16 all rows and 16 columns.  A is [rows, K], the rows in the sorted
-// order.  K is walked in steps of 64 through a ring of STAGES stages filled by 16-byte cp.async (the
-// rows of A and of the weights alike), so that a CTA always has several stages of weights in
-// flight: a step of few rows is a stream of the experts' weights.  Every element's sum runs over
+// of 4 warps takes a tile of BM rows x 64 columns of one expert.  BM = 16 (steps of few rows: a
+// stream of the experts' weights): the warps split the columns, 16 each.  BM = 64: 2 x 2 warps of
+// 32 rows x 32 columns.  BM = 128: the warps split the rows, 32 rows x 64 columns each, so that a
+// fragment of the weights read from shared memory feeds two products and a fragment of A eight
+// (sixteen with gate and up).  A is [rows, K], the rows in the sorted order.  K is walked in
+// steps of 64 through a ring of STAGES stages filled by 16-byte cp.async (the rows of A and of the
+// weights alike), so that a CTA always has several stages in flight.  Every element's sum runs over
 // K in the same order whatever tile the row is in.
-template <bool GATE_UP, int BM, int STAGES>
+template <bool GATE_UP, int BM, int WARPS_M, int STAGES>
 __global__ void __launch_bounds__(128)
 moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, const bf16* __restrict__ W1, void* __restrict__ out_,
                        const int* __restrict__ plan, const int* __restrict__ row_pair, int experts, int N, int K, float limit,
@@ -255,7 +257,9 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
   pdl_trigger();
   pdl_wait();
   constexpr int BN = 64, BK = 64, P = BK * 2 + 16;            // pitch in bytes: an odd number of 16-byte chunks
-  constexpr int WN = BM == 64 ? 64 : 16;                      // columns a warp holds
+  constexpr int WARPS_N = 4 / WARPS_M, WM = BM / WARPS_M, WN = BN / WARPS_N;
+  constexpr int MI = WM / 16, NJ = WN / 8;
+  static_assert(WM % 16 == 0 && NJ % 2 == 0, "a warp holds whole 16-row blocks and pairs of 8-column blocks");
   constexpr int A_BYTES = BM * P, W_BYTES = BN * P, STAGE = A_BYTES + (GATE_UP ? 2 : 1) * W_BYTES;
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
@@ -286,13 +290,17 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
       }
     }
   };
-  const int row_base = BM == 64 ? warp * 16 : 0, col_base = BM == 64 ? 0 : warp * 16;
-  float acc0[WN / 8][4], acc1[GATE_UP ? WN / 8 : 1][4];
+  const int row_base = (warp / WARPS_N) * WM, col_base = (warp % WARPS_N) * WN;
+  float acc0[MI][NJ][4], acc1[GATE_UP ? MI : 1][GATE_UP ? NJ : 1][4];
 #pragma unroll
-  for (int j = 0; j < WN / 8; ++j) acc0[j][0] = acc0[j][1] = acc0[j][2] = acc0[j][3] = 0.f;
+  for (int i = 0; i < MI; ++i)
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) acc0[i][j][0] = acc0[i][j][1] = acc0[i][j][2] = acc0[i][j][3] = 0.f;
   if (GATE_UP) {
 #pragma unroll
-    for (int j = 0; j < WN / 8; ++j) acc1[j][0] = acc1[j][1] = acc1[j][2] = acc1[j][3] = 0.f;
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) acc1[i][j][0] = acc1[i][j][1] = acc1[i][j][2] = acc1[i][j][3] = 0.f;
   }
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
@@ -309,41 +317,55 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
     const unsigned char* Ws1 = Ws0 + W_BYTES;
 #pragma unroll
     for (int kk = 0; kk < BK / 16; ++kk) {
-      unsigned a[4];
-      ldmatrix_x4(a, st + (row_base + (lane & 15)) * P + (kk * 16 + 8 * (lane >> 4)) * 2);
+      unsigned a[MI][4];
 #pragma unroll
-      for (int j = 0; j < WN / 8; ++j) {
-        unsigned b[2];
-        ldmatrix_x2(b, Ws0 + (col_base + j * 8 + (lane & 7)) * P + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2);
-        mma_bf16(acc0[j], a, b[0], b[1]);
+      for (int i = 0; i < MI; ++i) ldmatrix_x4(a[i], st + (row_base + i * 16 + (lane & 15)) * P + (kk * 16 + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int jp = 0; jp < NJ / 2; ++jp) {
+        // two 8-column blocks at a time: (columns 0-7, k 0-7), (0-7, k 8-15), (8-15, k 0-7), (8-15, k 8-15)
+        const int off = (col_base + jp * 16 + (lane & 7) + 8 * (lane >> 4)) * P + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2;
+        unsigned b[4];
+        ldmatrix_x4(b, Ws0 + off);
+#pragma unroll
+        for (int i = 0; i < MI; ++i) {
+          mma_bf16(acc0[i][2 * jp], a[i], b[0], b[1]);
+          mma_bf16(acc0[i][2 * jp + 1], a[i], b[2], b[3]);
+        }
         if (GATE_UP) {
-          ldmatrix_x2(b, Ws1 + (col_base + j * 8 + (lane & 7)) * P + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2);
-          mma_bf16(acc1[j], a, b[0], b[1]);
+          ldmatrix_x4(b, Ws1 + off);
+#pragma unroll
+          for (int i = 0; i < MI; ++i) {
+            mma_bf16(acc1[i][2 * jp], a[i], b[0], b[1]);
+            mma_bf16(acc1[i][2 * jp + 1], a[i], b[2], b[3]);
+          }
         }
       }
     }
   }
   cp_async_wait<0>();
 #pragma unroll
-  for (int j = 0; j < WN / 8; ++j) {
+  for (int i = 0; i < MI; ++i) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int r = row_base + g + 8 * half;
-      if (src_row[r] < 0) continue;
-      const int gn = n0 + col_base + j * 8 + 2 * t;
-      if (gn >= N) continue;
-      const float v0 = acc0[j][2 * half], v1 = acc0[j][2 * half + 1];
-      if (GATE_UP) {
-        const float g0 = fminf(v0, limit), g1 = fminf(v1, limit);
-        const float u0 = fminf(fmaxf(acc1[j][2 * half], -limit), limit), u1 = fminf(fmaxf(acc1[j][2 * half + 1], -limit), limit);
-        const float y0 = g0 / (1.0f + expf(-alpha * g0)) * (u0 + 1.0f), y1 = g1 / (1.0f + expf(-alpha * g1)) * (u1 + 1.0f);
-        bf16* o = reinterpret_cast<bf16*>(out_) + (size_t)(m0 + r) * N + gn;
-        if (gn + 1 < N && N % 2 == 0) *reinterpret_cast<unsigned*>(o) = pack_bf16(y0, y1);
-        else { o[0] = __float2bfloat16_rn(y0); if (gn + 1 < N) o[1] = __float2bfloat16_rn(y1); }
-      } else {
-        float* o = reinterpret_cast<float*>(out_) + (size_t)(m0 + r) * N + gn;
-        o[0] = v0;
-        if (gn + 1 < N) o[1] = v1;
+    for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = row_base + i * 16 + g + 8 * half;
+        if (src_row[r] < 0) continue;
+        const int gn = n0 + col_base + j * 8 + 2 * t;
+        if (gn >= N) continue;
+        const float v0 = acc0[i][j][2 * half], v1 = acc0[i][j][2 * half + 1];
+        if (GATE_UP) {
+          const float g0 = fminf(v0, limit), g1 = fminf(v1, limit);
+          const float u0 = fminf(fmaxf(acc1[i][j][2 * half], -limit), limit), u1 = fminf(fmaxf(acc1[i][j][2 * half + 1], -limit), limit);
+          const float y0 = g0 / (1.0f + expf(-alpha * g0)) * (u0 + 1.0f), y1 = g1 / (1.0f + expf(-alpha * g1)) * (u1 + 1.0f);
+          bf16* o = reinterpret_cast<bf16*>(out_) + (size_t)(m0 + r) * N + gn;
+          if (gn + 1 < N && N % 2 == 0) *reinterpret_cast<unsigned*>(o) = pack_bf16(y0, y1);
+          else { o[0] = __float2bfloat16_rn(y0); if (gn + 1 < N) o[1] = __float2bfloat16_rn(y1); }
+        } else {
+          float* o = reinterpret_cast<float*>(out_) + (size_t)(m0 + r) * N + gn;
+          o[0] = v0;
+          if (gn + 1 < N) o[1] = v1;
+        }
       }
     }
   }
@@ -408,13 +430,13 @@ Q25_EXPORT int q25_moe_sort(const int* topk_idx, const int* counts, int* cursor,
   return launch_status();
 }
 
-template <bool GATE_UP, int BM, int STAGES>
+template <bool GATE_UP, int BM, int WARPS_M, int STAGES>
 static int moe_grouped_mma_shape(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
                                  int tiles, int experts, int N, int K, float limit, float alpha, cudaStream_t s) {
   constexpr int SMEM = STAGES * (BM + (GATE_UP ? 128 : 64)) * (64 * 2 + 16);
-  const cudaError_t e = cudaFuncSetAttribute(moe_grouped_mma_kernel<GATE_UP, BM, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  const cudaError_t e = cudaFuncSetAttribute(moe_grouped_mma_kernel<GATE_UP, BM, WARPS_M, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   if (e != cudaSuccess) return (int)e;
-  launch(moe_grouped_mma_kernel<GATE_UP, BM, STAGES>, dim3((N + 63) / 64, tiles), dim3(128), SMEM, s, (const bf16*)A, (const bf16*)W0,
+  launch(moe_grouped_mma_kernel<GATE_UP, BM, WARPS_M, STAGES>, dim3((N + 63) / 64, tiles), dim3(128), SMEM, s, (const bf16*)A, (const bf16*)W0,
          (const bf16*)W1, out, plan, row_pair, experts, N, K, limit, alpha);
   return launch_status();
 }
@@ -425,8 +447,11 @@ static int moe_grouped_mma(const void* A, const void* W0, const void* W1, void* 
                            int n_pairs, int experts, int N, int K, float limit, float alpha, int tile, void* stream) {
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
   cudaStream_t s = (cudaStream_t)stream;
-  if (tile == 16) return moe_grouped_mma_shape<GATE_UP, 16, 4>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
-  if (tile == 64) return moe_grouped_mma_shape<GATE_UP, 64, 3>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
+  if (tile == 16) return moe_grouped_mma_shape<GATE_UP, 16, 1, 4>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
+  // two stages for the large tiles: three or four CTAs then share an SM (12 to 16 warps), which hides the fixed latencies between
+  // a fragment's load and its products better than a third stage does (gate and up at 4,096 rows: 268 us with three stages)
+  if (tile == 64) return moe_grouped_mma_shape<GATE_UP, 64, 2, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
+  if (tile == 128) return moe_grouped_mma_shape<GATE_UP, 128, 4, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
   return (int)cudaErrorInvalidValue;
 }
 

@@ -113,7 +113,9 @@ class RoutedGLU(FeedForward):
     def forward(self, ctx, h):
         n, top, experts = h.shape[0], self.top, self.experts
         pairs = n * top
-        tile = 16 if pairs <= 16 * experts else 64          # rows of a tile of the grouped products; from the step's shape alone
+        # rows of a tile of the grouped products, from the step's shape alone: 16 while an expert gets 16
+        # rows on average (the product is then a stream of weights), 128 from 128 on (bfloat16)
+        tile = 16 if pairs <= 16 * experts else (128 if pairs >= 128 * experts and ctx.dtype == torch.bfloat16 else 64)
         rows = kernels.moe_max_rows(pairs, experts, tile)
         dev = h.device
         shared = None
