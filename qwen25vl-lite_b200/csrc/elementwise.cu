@@ -244,16 +244,31 @@ __global__ void add_norm_groups_kernel(float* __restrict__ x, const T* __restric
 
 // Gated linear unit with clamped branches: gu is [n, 2*inter], gate in the first half of a row, up
 // in the second; g = min(g, limit), u = clamp(u, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter, float limit, float alpha) {
   pdl_trigger();
   pdl_wait();
-  const size_t total = (size_t)n * inter;
+  constexpr int STEP = VEC ? 4 : 1;                     // VEC: inter is a multiple of 4 and the rows start on 16-byte boundaries
+  const size_t total = (size_t)n * inter / STEP;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t row = i / inter, c = i % inter;
-    const float g = fminf(to_f32(gu[row * 2 * inter + c]), limit);
-    const float u = fminf(fmaxf(to_f32(gu[row * 2 * inter + inter + c]), -limit), limit);
-    out[i] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    const size_t row = i * STEP / inter, c = i * STEP % inter;
+    const T* g_at = gu + row * 2 * inter + c;
+    float g[4], u[4];
+    if (VEC) {
+      const float4 gv = load4<T>(g_at), uv = load4<T>(g_at + inter);
+      g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+      u[0] = uv.x; u[1] = uv.y; u[2] = uv.z; u[3] = uv.w;
+    } else {
+      g[0] = to_f32(g_at[0]);
+      u[0] = to_f32(g_at[inter]);
+    }
+#pragma unroll
+    for (int k = 0; k < STEP; ++k) {
+      const float gg = fminf(g[k], limit), uu = fminf(fmaxf(u[k], -limit), limit);
+      g[k] = gg / (1.0f + expf(-alpha * gg)) * (uu + 1.0f);
+    }
+    if (VEC) store4<T>(out + i * 4, make_float4(g[0], g[1], g[2], g[3]));
+    else out[i] = from_f32<T>(g[0]);
   }
 }
 
@@ -301,11 +316,13 @@ static int add_norm_groups(float* x, const void* delta, const float* dw, float d
 template <typename T>
 static int glu_clamped(const void* gu, void* out, int n, int inter, float limit, float alpha, void* stream) {
   if (n <= 0) return 0;
-  const size_t total = (size_t)n * inter;
+  const bool vec = inter % 4 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15);
+  const size_t total = (size_t)n * inter / (vec ? 4 : 1);
   size_t blocks = (total + 255) / 256;
   const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
   if (blocks > most) blocks = most;
-  launch(glu_clamped_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha);
+  if (vec) launch(glu_clamped_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha);
+  else launch(glu_clamped_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha);
   return launch_status();
 }
 

@@ -22,53 +22,73 @@
 #define MOE_MAX_EXPERTS 256
 #define MOE_MAX_TOP 16
 
-// One block of 4 warps per token: the token's row is widened to float in shared memory once; each
-// warp takes every fourth expert (and the last warp's turn the shared expert's gate) and forms
-// its logit with the lanes striding over the channels four at a time, then a butterfly: an order
-// that depends on the sizes alone.  Warp 0 then picks the `top` largest (ties to the lower index).
-template <typename T>
-__global__ void __launch_bounds__(128)
+// One block of 8 warps per TOK tokens (4 in steps of many tokens, where a row of the router read from
+// cache then serves four tokens; 1 otherwise): the tokens' rows are widened to float in shared memory
+// once; each warp takes every eighth expert (and in its turn the shared expert's gate) and forms the
+// logits with the lanes striding over the channels four at a time, then a butterfly: an order that
+// depends on the sizes alone, whatever the step.  Then a warp per token picks the `top` largest
+// (ties to the lower index).
+template <typename T, int TOK>
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ shared_gate,
                  int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ sg,
                  int* __restrict__ counts, int n_tokens, int hidden, int experts, int top) {
   pdl_trigger();
   pdl_wait();
-  extern __shared__ __align__(16) float route_smem[];       // hidden floats, then MOE_MAX_EXPERTS + 1 logits
+  extern __shared__ __align__(16) float route_smem[];       // TOK rows of hidden floats, then TOK x (MOE_MAX_EXPERTS + 1) logits
+  const int pitch = (hidden + 3) & ~3;
   float* xs = route_smem;
-  float* zs = route_smem + ((hidden + 3) & ~3);
+  float* zs = route_smem + TOK * pitch;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x;
-  const T* row = h + (size_t)n * hidden;
-  for (int c = threadIdx.x; c < hidden; c += 128) xs[c] = to_f32(row[c]);
+  const int n0 = blockIdx.x * TOK;
+  for (int i = 0; i < TOK; ++i) {
+    const int n = min(n0 + i, n_tokens - 1);
+    const T* row = h + (size_t)n * hidden;
+    for (int c = threadIdx.x; c < hidden; c += 256) xs[i * pitch + c] = to_f32(row[c]);
+  }
   __syncthreads();
   const int n_dots = experts + (shared_gate ? 1 : 0);
   const bool vec = hidden % 4 == 0 && !(((uintptr_t)router | (uintptr_t)shared_gate) & 15);
-  for (int e = warp; e < n_dots; e += 4) {
+  for (int e = warp; e < n_dots; e += 8) {
     const float* w = e < experts ? router + (size_t)e * hidden : shared_gate;
-    float acc = 0.f;
+    float acc[TOK];
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) acc[i] = 0.f;
     if (vec) {
-#pragma unroll 4
+#pragma unroll 8
       for (int c = lane * 4; c < hidden; c += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(w + c), xv = *reinterpret_cast<const float4*>(xs + c);
-        acc = fmaf(wv.x, xv.x, acc);
-        acc = fmaf(wv.y, xv.y, acc);
-        acc = fmaf(wv.z, xv.z, acc);
-        acc = fmaf(wv.w, xv.w, acc);
+        const float4 wv = *reinterpret_cast<const float4*>(w + c);
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+          const float4 xv = *reinterpret_cast<const float4*>(xs + i * pitch + c);
+          acc[i] = fmaf(wv.x, xv.x, acc[i]);
+          acc[i] = fmaf(wv.y, xv.y, acc[i]);
+          acc[i] = fmaf(wv.z, xv.z, acc[i]);
+          acc[i] = fmaf(wv.w, xv.w, acc[i]);
+        }
       }
     } else {
-      for (int c = lane; c < hidden; c += 32) acc = fmaf(w[c], xs[c], acc);
+      for (int c = lane; c < hidden; c += 32) {
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) acc[i] = fmaf(w[c], xs[i * pitch + c], acc[i]);
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) zs[e] = acc;
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) {
+      const float z = warp_sum(acc[i]);
+      if (lane == 0) zs[i * (MOE_MAX_EXPERTS + 1) + e] = z;
+    }
   }
   __syncthreads();
-  if (warp != 0) return;
-  if (shared_gate && lane == 0) sg[n] = 1.0f / (1.0f + expf(-zs[experts]));
+  if (warp >= TOK || n0 + warp >= n_tokens) return;
+  const int n = n0 + warp;
+  float* z_row = zs + warp * (MOE_MAX_EXPERTS + 1);
+  if (shared_gate && lane == 0) sg[n] = 1.0f / (1.0f + expf(-z_row[experts]));
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
     for (int e = lane; e < experts; e += 32) {
-      const float z = zs[e];
+      const float z = z_row[e];
       if (z > best) { best = z; arg = e; }
     }
 #pragma unroll
@@ -80,7 +100,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
     if (lane == 0) {
       topk_idx[(size_t)n * top + k] = arg;
       topk_w[(size_t)n * top + k] = 1.0f / (1.0f + expf(-best));
-      zs[arg] = -INFINITY;
+      z_row[arg] = -INFINITY;
       atomicAdd(&counts[arg], 1);
     }
     __syncwarp();
@@ -378,13 +398,35 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
                                    const T* __restrict__ shared, T* __restrict__ out, int n_tokens, int hidden, int top) {
   pdl_trigger();
   pdl_wait();
-  const size_t total = (size_t)n_tokens * hidden;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int n = (int)(i / hidden), c = (int)(i % hidden);
-    float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc += y[(size_t)pair_row[(size_t)n * top + k] * hidden + c];
-    if (shared) acc = fmaf(sg[n], to_f32(shared[i]), acc);
-    out[i] = from_f32<T>(acc);
+  // a block per token: its rows are looked up once; four channels at a time where the width allows
+  const int n = blockIdx.x;
+  __shared__ int rows[MOE_MAX_TOP];
+  if (threadIdx.x < top) rows[threadIdx.x] = pair_row[(size_t)n * top + threadIdx.x];
+  __syncthreads();
+  const float gate = shared ? sg[n] : 0.f;
+  if (hidden % 4 == 0 && !(((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out) & 15)) {
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < top; ++k) {
+        const float4 v = *reinterpret_cast<const float4*>(y + (size_t)rows[k] * hidden + c);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      if (shared) {
+        float s4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s4[i] = to_f32(shared[(size_t)n * hidden + c + i]);
+        acc.x = fmaf(gate, s4[0], acc.x); acc.y = fmaf(gate, s4[1], acc.y); acc.z = fmaf(gate, s4[2], acc.z); acc.w = fmaf(gate, s4[3], acc.w);
+      }
+      T* o = out + (size_t)n * hidden + c;
+      o[0] = from_f32<T>(acc.x); o[1] = from_f32<T>(acc.y); o[2] = from_f32<T>(acc.z); o[3] = from_f32<T>(acc.w);
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float acc = 0.f;
+      for (int k = 0; k < top; ++k) acc += y[(size_t)rows[k] * hidden + c];
+      if (shared) acc = fmaf(gate, to_f32(shared[(size_t)n * hidden + c]), acc);
+      out[(size_t)n * hidden + c] = from_f32<T>(acc);
+    }
   }
 }
 
@@ -394,20 +436,30 @@ Q25_EXPORT int q25_moe_max_rows(int n_pairs, int experts, int tile) {
   return most_tiles * tile;
 }
 
+template <typename T, int TOK>
+static int moe_route_shape(const void* h, const float* router, const float* shared_gate, int* topk_idx, float* topk_w, float* sg,
+                           int* counts, int n_tokens, int hidden, int experts, int top, cudaStream_t stream) {
+  const size_t smem = (size_t)TOK * (((hidden + 3) & ~3) + MOE_MAX_EXPERTS + 1) * sizeof(float);
+  if (smem > 200 * 1024) return -1;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(moe_route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)h, router, shared_gate, topk_idx,
+         topk_w, sg, counts, n_tokens, hidden, experts, top);
+  return launch_status();
+}
+
 template <typename T>
 static int moe_route(const void* h, const float* router, const float* shared_gate, int* topk_idx, float* topk_w, float* sg,
                      int* counts, int n_tokens, int hidden, int experts, int top, void* stream) {
   if (n_tokens <= 0) return 0;
   if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts || top > MOE_MAX_TOP) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)(((hidden + 3) & ~3) + MOE_MAX_EXPERTS + 4) * sizeof(float);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-  if (smem > 48 * 1024) {
-    const cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
-  launch(moe_route_kernel<T>, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, (const T*)h, router, shared_gate, topk_idx,
-         topk_w, sg, counts, n_tokens, hidden, experts, top);
-  return launch_status();
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc = -1;
+  if (n_tokens >= 512) rc = moe_route_shape<T, 4>(h, router, shared_gate, topk_idx, topk_w, sg, counts, n_tokens, hidden, experts, top, s);
+  if (rc == -1) rc = moe_route_shape<T, 1>(h, router, shared_gate, topk_idx, topk_w, sg, counts, n_tokens, hidden, experts, top, s);
+  return rc == -1 ? (int)cudaErrorInvalidValue : rc;
 }
 
 Q25_EXPORT int q25_moe_route_f32(const void* h, const float* r, const float* g, int* ti, float* tw, float* sg, int* counts, int n,
@@ -511,12 +563,8 @@ template <typename T>
 static int moe_combine(const float* y, const int* pair_row, const float* sg, const void* shared, void* out, int n_tokens, int hidden,
                        int top, void* stream) {
   if (n_tokens <= 0) return 0;
-  const size_t total = (size_t)n_tokens * hidden;
-  size_t blocks = (total + 255) / 256;
-  const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
-  if (blocks > most) blocks = most;
-  launch(moe_combine_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, y, pair_row, sg, (const T*)shared, (T*)out,
-         n_tokens, hidden, top);
+  launch(moe_combine_kernel<T>, dim3(n_tokens), dim3(hidden >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, y, pair_row, sg,
+         (const T*)shared, (T*)out, n_tokens, hidden, top);
   return launch_status();
 }
 Q25_EXPORT int q25_moe_combine_f32(const float* y, const int* pr, const float* sg, const void* sh, void* out, int n, int h, int top, void* s) {

@@ -26,24 +26,24 @@ template <typename T>
 __global__ void rglru_conv_kernel(const T* __restrict__ yx, int ld, int x_off, const float* __restrict__ conv_w,
                                   const float* __restrict__ conv_b, const float* __restrict__ state,
                                   const int* __restrict__ token_seq, const int* __restrict__ cu_q,
-                                  const int* __restrict__ slot_ids, float* __restrict__ u, int n_tokens, int width, int taps) {
+                                  const int* __restrict__ slot_ids, float* __restrict__ u, int row0, int width, int taps) {
   pdl_trigger();
   pdl_wait();
-  const size_t total = (size_t)n_tokens * width;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int n = (int)(i / width), c = (int)(i % width);
-    const int seq = token_seq[n];
-    const int first = cu_q[seq];
-    const int t = n - first;
-    const float* hist = state + ((size_t)slot_ids[seq] * taps + 1) * width + c;      // rows 1 .. taps-1
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int rel = t - (taps - 1) + j;
-      const float v = rel >= 0 ? to_f32(yx[(size_t)(first + rel) * ld + x_off + c]) : hist[(size_t)(taps - 1 + rel) * width];
-      acc = fmaf(conv_w[(size_t)c * taps + j], v, acc);
-    }
-    u[i] = acc + conv_b[c];
+  // a row of blocks per token: what depends on the token alone is looked up once
+  const int n = row0 + blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const int seq = token_seq[n];
+  const int first = cu_q[seq];
+  const int t = n - first;
+  const float* hist = state + ((size_t)slot_ids[seq] * taps + 1) * width + c;      // rows 1 .. taps-1
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int rel = t - (taps - 1) + j;
+    const float v = rel >= 0 ? to_f32(yx[(size_t)(first + rel) * ld + x_off + c]) : hist[(size_t)(taps - 1 + rel) * width];
+    acc = fmaf(conv_w[(size_t)c * taps + j], v, acc);
   }
+  u[(size_t)n * width + c] = acc + conv_b[c];
 }
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
@@ -155,6 +155,7 @@ __global__ void rglru_chunk_kernel(const float* __restrict__ a, const float* __r
   if (chunk == 0) sums[(size_t)n_seqs * max_chunks * 2 * width + (size_t)seq * width + c] = state[(size_t)slot_ids[seq] * taps * width + c];
   const int t0 = chunk * RG_CHUNK, t1 = min(n, t0 + RG_CHUNK);
   float A = 1.f, B = 0.f;
+#pragma unroll 8
   for (int t = t0; t < t1; ++t) {
     const size_t at = (size_t)(first + t) * width + c;
     const float av = a[at];
@@ -179,11 +180,13 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __re
   if (c >= width || chunk * RG_CHUNK >= n) return;
   float* st = state + (size_t)slot_ids[seq] * taps * width + c;
   float S = sums ? sums[(size_t)n_seqs * max_chunks * 2 * width + (size_t)seq * width + c] : st[0];
+#pragma unroll 8
   for (int j = 0; j < chunk; ++j) {
     const size_t at = ((size_t)seq * max_chunks + j) * 2 * width + c;
     S = fmaf(sums[at], S, sums[at + width]);
   }
   const int t0 = chunk * RG_CHUNK, t1 = min(n, t0 + RG_CHUNK);
+#pragma unroll 8
   for (int t = t0; t < t1; ++t) {
     const size_t at = (size_t)(first + t) * width + c;
     S = fmaf(a[at], S, bx[at]);
@@ -210,12 +213,12 @@ static int rglru_conv(const void* yx, int ld, int x_off, const float* conv_w, co
                       void* stream) {
   if (n_tokens <= 0) return 0;
   if (taps < 1 || taps > RG_MAX_TAPS) return (int)cudaErrorInvalidValue;
-  const size_t total = (size_t)n_tokens * width;
-  size_t blocks = (total + 255) / 256;
-  const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
-  if (blocks > most) blocks = most;
-  launch(rglru_conv_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)yx, ld, x_off, conv_w, conv_b,
-         state, token_seq, cu_q, slot_ids, u, n_tokens, width, taps);
+  if (n_tokens > 65535 * 32) return (int)cudaErrorInvalidValue;
+  for (int at = 0; at < n_tokens; at += 65535) {                  // the grid's second dimension ends at 65,535
+    const int rows = n_tokens - at < 65535 ? n_tokens - at : 65535;
+    launch(rglru_conv_kernel<T>, dim3((width + 255) / 256, rows), dim3(256), 0, (cudaStream_t)stream, (const T*)yx, ld, x_off, conv_w,
+           conv_b, state, token_seq, cu_q, slot_ids, u, at, width, taps);
+  }
   return launch_status();
 }
 

@@ -24,7 +24,7 @@ def group_norm(v, w, groups, eps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden,groups,dgroups", [(96, 3, 3), (320, 1, 4), (1024, 8, 2)])
+@pytest.mark.parametrize("hidden,groups,dgroups", [(96, 3, 3), (384, 1, 4), (1024, 8, 2)])
 def test_add_norm_groups(dtype, hidden, groups, dgroups):
     g = torch.Generator(device=DEV).manual_seed(1)
     n = 9
@@ -101,7 +101,7 @@ def recurrence_reference(yx, width, conv_w, conv_b, ra, ra_b, ri, ri_b, lam, gai
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,blocks,taps", [(64, 4, 3), (160, 1, 2), (96, 3, 1), (256, 2, 4)])
+@pytest.mark.parametrize("width,blocks,taps", [(64, 4, 3), (176, 1, 2), (96, 3, 1), (256, 2, 4)])
 def test_recurrence_in_portions_with_state(dtype, width, blocks, taps):
     """Two requests of unequal length in three steps (portions of 1, 2 and many tokens, the second
     request absent from the middle step), in slots 2 and 0 of three: the state carries S and the
@@ -146,7 +146,7 @@ def test_recurrence_in_portions_with_state(dtype, width, blocks, taps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,experts,top,hidden,ff", [(1, 4, 1, 64, 24), (7, 6, 2, 96, 40), (150, 5, 3, 128, 48), (300, 8, 1, 320, 64),
+@pytest.mark.parametrize("n,experts,top,hidden,ff", [(1, 4, 1, 64, 24), (7, 6, 2, 96, 40), (150, 5, 3, 128, 48), (300, 8, 1, 352, 72),
                                                      (700, 4, 1, 72, 40), (33, 3, 2, 100, 30)])
 def test_routed_experts(dtype, n, experts, top, hidden, ff):
     """From one token to hundreds per expert (row tiles of 16, 64 and 128), one to three choices, and
@@ -245,7 +245,7 @@ def attention_case(dtype, nq, nkv, dk, dv, page_size, window, keep, entries, see
     return out.double().reshape(n_tokens, nq, dv), ref
 
 
-SHAPES = [(8, 2, 64, 64), (4, 4, 32, 64), (6, 1, 128, 64), (3, 3, 48, 80), (8, 2, 64, 128)]
+SHAPES = [(6, 2, 64, 64), (4, 4, 32, 64), (6, 1, 128, 64), (3, 3, 48, 80), (8, 2, 64, 128)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

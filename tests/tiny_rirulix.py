@@ -60,11 +60,11 @@ R2 = _config(300, 128, 768, 1, 1e-6, [
     {"type": "rglru", "mixer": {"width": 64, "blocks": 1, "conv": 2}, "mlp": _moe(5, 3, 48, 2.0)},
 ])
 # 3 layers, width 256, 4 norm groups; keys of 128 with values of 64, then keys and values of 64 with
-# 8 query heads, value mixing between them; windows beyond a hundred tokens; 8 experts of which 1.
+# 6 query heads, value mixing between them; windows beyond a hundred tokens; 8 experts of which 1.
 R3 = _config(160, 256, 1024, 4, 1e-6, [
-    {"type": "attention", "mixer": _attn(4, 2, 128, 64, 0.09, 130, 4, True), "mlp": _moe(8, 1, 64, 2.0, (96, 1.0))},
-    {"type": "rglru", "mixer": {"width": 192, "blocks": 3, "conv": 4}, "mlp": _moe(8, 1, 64, 2.0, (96, 1.0))},
-    {"type": "attention", "mixer": _attn(8, 2, 64, 64, 0.125, 200, 7, True), "mlp": _moe(8, 1, 64, 2.0, (96, 1.0))},
+    {"type": "attention", "mixer": _attn(4, 2, 128, 64, 0.09, 130, 6, True), "mlp": _moe(8, 1, 72, 1.75, (88, 1.25))},
+    {"type": "rglru", "mixer": {"width": 192, "blocks": 3, "conv": 4}, "mlp": _moe(8, 1, 72, 1.75, (88, 1.25))},
+    {"type": "attention", "mixer": _attn(6, 2, 64, 64, 0.11, 200, 7, True), "mlp": _moe(8, 1, 72, 1.75, (88, 1.25))},
 ])
 
 TINY = {"R1": (R1, 11, 16), "R2": (R2, 12, 8), "R3": (R3, 13, 16)}      # config, weight seed, page size
