@@ -123,6 +123,49 @@ rglru_gates_kernel(const float* __restrict__ u, const float* __restrict__ ra, co
   }
 }
 
+// The same for steps of few tokens (decode): a CTA takes 16 tokens x 16 channels of one block and
+// brings the whole depth of the product into shared memory at once, so that all its loads are in
+// flight together instead of a chain of tiles; one thread per (token, channel), the same FMA chains
+// in the same order as above.  Dynamic shared memory: 3 x bw x 17 floats.
+__global__ void __launch_bounds__(256)
+rglru_gates_small_kernel(const float* __restrict__ u, const float* __restrict__ ra, const float* __restrict__ ra_b,
+                         const float* __restrict__ ri, const float* __restrict__ ri_b, const float* __restrict__ lam,
+                         float gain, float* __restrict__ a_out, float* __restrict__ bx_out, int n_tokens, int width, int bw) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float gates_smem[];
+  float* Us = gates_smem;                  // [bw][17]
+  float* As = Us + (size_t)bw * 17;
+  float* Is = As + (size_t)bw * 17;
+  const int b = blockIdx.z, m0 = blockIdx.y * 16, n0 = blockIdx.x * 16;
+  const float* Wa = ra + (size_t)b * bw * bw;
+  const float* Wi = ri + (size_t)b * bw * bw;
+  for (int e = threadIdx.x; e < 16 * bw; e += 256) {
+    const int r = e / bw, k = e % bw;                     // consecutive threads read consecutive k
+    const int gm = m0 + r, gn = n0 + r;
+    Us[k * 17 + r] = gm < n_tokens ? u[(size_t)gm * width + b * bw + k] : 0.f;
+    As[k * 17 + r] = gn < bw ? Wa[(size_t)gn * bw + k] : 0.f;
+    Is[k * 17 + r] = gn < bw ? Wi[(size_t)gn * bw + k] : 0.f;
+  }
+  __syncthreads();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc_a = 0.f, acc_i = 0.f;
+  for (int k = 0; k < bw; ++k) {
+    const float uu = Us[k * 17 + ty];
+    acc_a = fmaf(uu, As[k * 17 + tx], acc_a);
+    acc_i = fmaf(uu, Is[k * 17 + tx], acc_i);
+  }
+  const int gm = m0 + ty, gn = n0 + tx;
+  if (gm >= n_tokens || gn >= bw) return;
+  const int c = b * bw + gn;
+  const float r = sigmoid_f(acc_a + ra_b[c]);
+  const float g = sigmoid_f(acc_i + ri_b[c]);
+  const float log_a = -gain * r * softplus_f(lam[c]);
+  const size_t at = (size_t)gm * width + c;
+  a_out[at] = expf(log_a);
+  bx_out[at] = sqrtf(-expm1f(2.0f * log_a)) * g * u[at];
+}
+
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -258,7 +301,15 @@ Q25_EXPORT int q25_rglru_gates(const float* u, const float* ra, const float* ra_
   if (n_tokens <= 0) return 0;
   if (blocks <= 0 || width % blocks) return (int)cudaErrorInvalidValue;
   const int bw = width / blocks;
-  if (n_tokens <= 16) {
+  const size_t small_smem = (size_t)3 * bw * 17 * sizeof(float);
+  if (n_tokens <= 128 && small_smem <= 160 * 1024) {
+    if (small_smem > 48 * 1024) {
+      const cudaError_t e = cudaFuncSetAttribute(rglru_gates_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    launch(rglru_gates_small_kernel, dim3((bw + 15) / 16, (n_tokens + 15) / 16, blocks), dim3(256), small_smem, (cudaStream_t)stream, u, ra,
+           ra_b, ri, ri_b, lam, gain, a_out, bx_out, n_tokens, width, bw);
+  } else if (n_tokens <= 16) {
     launch(rglru_gates_kernel<16, 64, 16, 1, 4>, dim3((bw + 63) / 64, (n_tokens + 15) / 16, blocks), dim3(256), 0, (cudaStream_t)stream,
            u, ra, ra_b, ri, ri_b, lam, gain, a_out, bx_out, n_tokens, width, bw);
   } else {

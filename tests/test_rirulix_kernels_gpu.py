@@ -105,21 +105,22 @@ def recurrence_reference(yx, width, conv_w, conv_b, ra, ra_b, ri, ri_b, lam, gai
 def test_recurrence_in_portions_with_state(dtype, width, blocks, taps):
     """Two requests of unequal length in three steps (portions of 1, 2 and many tokens, the second
     request absent from the middle step), in slots 2 and 0 of three: the state carries S and the
-    convolution's last inputs, and the result is the whole sequence's.  The last step's 100 tokens
-    are scanned in four chunks beside an entry of one chunk."""
+    convolution's last inputs, and the result is the whole sequence's.  The last step's 260 tokens
+    are scanned in nine chunks beside an entry of one chunk, and its gates come from the tiled
+    product where the small steps' come from the one that holds the whole depth at once."""
     g = torch.Generator(device=DEV).manual_seed(4)
     rnd = lambda *shape, scale=1.0: torch.randn(*shape, generator=g, device=DEV) * scale
     bw = width // blocks
     conv_w, conv_b = rnd(width, taps, scale=0.5), rnd(width, scale=0.1)
     ra, ra_b, ri, ri_b, lam = rnd(blocks, bw, bw, scale=0.3), rnd(blocks, bw), rnd(blocks, bw, bw, scale=0.3), rnd(blocks, bw), rnd(width)
-    lens = {"a": 103, "b": 9}
+    lens = {"a": 263, "b": 9}
     yx = {k: rnd(n, 2 * width).to(dtype) for k, n in lens.items()}
     want = {k: recurrence_reference(yx[k], width, conv_w, conv_b, ra, ra_b, ri, ri_b, lam, 8.0) for k in lens}
     state = torch.zeros(3, taps, width, device=DEV)
     slot = {"a": 2, "b": 0}
     done = {"a": 0, "b": 0}
     got = {"a": [], "b": []}
-    for step in ({"a": 1, "b": 2}, {"a": 2}, {"a": 100, "b": 7}):
+    for step in ({"a": 1, "b": 2}, {"a": 2}, {"a": 260, "b": 7}):
         names = list(step)
         rows = torch.cat([yx[k][done[k]:done[k] + step[k]] for k in names])
         n = rows.shape[0]
