@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Dict, Iterator, Tuple
+from typing import Any, Dict, Iterator, Optional, Tuple
 
 import torch
 
@@ -49,8 +49,10 @@ def random_tensors(model, seed: int, device="cpu") -> Iterator[Tuple[str, Any, t
 
 
 def write_random_model(model_dir: str, config_json: Dict[str, Any], seed: int, storage_dtype: str = "float32",
-                       prefix: str = "model.language_model.") -> str:
-    """Writes ``config.json`` and ``model.safetensors`` under ``model_dir``."""
+                       prefix: Optional[str] = None) -> str:
+    """Writes ``config.json`` and ``model.safetensors`` under ``model_dir``.  ``prefix`` goes before
+    every tensor name; by default the first one the architecture accepts (``model.language_model.``
+    for Qwen2.5-VL, as its releases have it; none for an architecture whose files carry none)."""
     from ..models.decoder import DecoderModel
 
     arch = resolve_architecture(config_json)
@@ -61,6 +63,8 @@ def write_random_model(model_dir: str, config_json: Dict[str, Any], seed: int, s
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as fh:
         json.dump(config_json, fh, indent=1)
     unprefixed = set(model.spec.unprefixed_names)
+    if prefix is None:
+        prefix = model.spec.name_prefixes[0] if model.spec.name_prefixes else ""
 
     def named():
         for name, _, t in random_tensors(model, seed):

@@ -90,6 +90,20 @@ def test_random_model_folder_loads_by_name(tmp_path):
         assert json.load(fh)["architecture"] == "Rirulix"
 
 
+def test_command_line_writes_a_folder_that_the_loader_accepts(tmp_path):
+    """``random-model`` through the program's own entry point; the names in the file are the ones the
+    model expects (no prefix for this architecture), which is what ``generate`` and ``replay`` load."""
+    from qwen25vl_lite.cli import main
+    from qwen25vl_lite.weights.loader import canonical_name
+
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(R3))
+    assert main(["random-model", "--config", str(config), "--out", str(tmp_path / "m"), "--seed", "5", "--storage-dtype", "bfloat16"]) == 0
+    model = build(R3)
+    names = set(read_safetensors(str(tmp_path / "m" / "model.safetensors")))
+    assert {canonical_name(n, model.spec)[0] for n in names} == set(model.expected_tensors()) == names
+
+
 def test_kept_first_pages_stay_while_the_window_releases():
     """Window 20, 5 kept tokens, pages of 4: pages 0 and 1 hold kept tokens and are never given back;
     the pages between them and the window are."""
