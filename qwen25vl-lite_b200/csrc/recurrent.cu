@@ -309,10 +309,6 @@ Q25_EXPORT int q25_rglru_gates(const float* u, const float* ra, const float* ra_
     }
     launch(rglru_gates_small_kernel, dim3((bw + 15) / 16, (n_tokens + 15) / 16, blocks), dim3(256), small_smem, (cudaStream_t)stream, u, ra,
            ra_b, ri, ri_b, lam, gain, a_out, bx_out, n_tokens, width, bw);
-  } else if (n_tokens >= 512) {
-    // many tokens: 8 x 4 elements a thread, so that a value read from shared memory feeds more products
-    launch(rglru_gates_kernel<128, 64, 16, 8, 4>, dim3((bw + 63) / 64, (n_tokens + 127) / 128, blocks), dim3(256), 0, (cudaStream_t)stream,
-           u, ra, ra_b, ri, ri_b, lam, gain, a_out, bx_out, n_tokens, width, bw);
   } else if (n_tokens <= 16) {
     launch(rglru_gates_kernel<16, 64, 16, 1, 4>, dim3((bw + 63) / 64, (n_tokens + 15) / 16, blocks), dim3(256), 0, (cudaStream_t)stream,
            u, ra, ra_b, ri, ri_b, lam, gain, a_out, bx_out, n_tokens, width, bw);

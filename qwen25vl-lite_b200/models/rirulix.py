@@ -20,7 +20,8 @@ GLU_ALPHA = 1.702           # g * sigmoid(1.702 g)
 
 def build_spec(cfg: RirulixConfig) -> ModelSpec:
     h = cfg.hidden_size
-    norm = lambda name: PartSpec("rmsnorm", dict(dim=h, eps=cfg.norm_eps, groups=cfg.norm_groups, name=name))
+    norm = lambda name, optional=False: PartSpec("rmsnorm", dict(dim=h, eps=cfg.norm_eps, groups=cfg.norm_groups, name=name,
+                                                                 optional=optional))
     layers = []
     value_source = None                 # (kv heads, value size) of the first layer that mixes values
     for i, layer in enumerate(cfg.layers):
@@ -40,13 +41,14 @@ def build_spec(cfg: RirulixConfig) -> ModelSpec:
             mixer = PartSpec("rglru", dict(hidden_size=h, width=m.width, blocks=m.blocks, conv=m.conv, gain=RGLRU_GAIN), "mix.")
         ffn = None
         names = ["norm1", "norm1b"]
+        unused = ["norm2", "norm2b"]         # of a layer without a feed-forward: accepted in a file, never run
         if layer.mlp is not None:
             f = layer.mlp
             ffn = PartSpec("routed_glu", dict(hidden_size=h, experts=f.experts, top=f.top, expert_size=f.ff, limit=f.limit,
                                               alpha=GLU_ALPHA, shared_size=f.shared_ff, shared_limit=f.shared_limit), "mlp.")
-            names += ["norm2", "norm2b"]
-        layers.append(LayerSpec(block="sandwich_residual", mixer=mixer, feed_forward=ffn, norms=tuple(norm(n) for n in names),
-                                prefix=f"l{i}."))
+            names, unused = names + unused, []
+        layers.append(LayerSpec(block="sandwich_residual", mixer=mixer, feed_forward=ffn,
+                                norms=tuple(norm(n) for n in names) + tuple(norm(n, True) for n in unused), prefix=f"l{i}."))
     return ModelSpec(
         embedding=PartSpec("learned_position_embedding", dict(vocab_size=cfg.vocab_size, hidden_size=h, max_positions=cfg.max_positions,
                                                               norm_eps=cfg.norm_eps, norm_groups=cfg.norm_groups,

@@ -124,8 +124,8 @@ class BiasedWindowAttention(Mixer):
         q, k, v, h = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim, self.num_kv_heads * self.value_dim, self.hidden_size
         specs = [TensorSpec("q", (q, h)), TensorSpec("q.b", (q,), "bias"), TensorSpec("k", (k, h)), TensorSpec("k.b", (k,), "bias"),
                  TensorSpec("v", (v, h)), TensorSpec("v.b", (v,), "bias")]
-        if self.value_mix is not None:
-            specs.append(TensorSpec("vmix", (), "fraction"))
+        # a layer that mixes nothing has no use for the scalar; a checkpoint that holds one all the same is accepted
+        specs.append(TensorSpec("vmix", (), "fraction", optional=self.value_mix is None))
         if self.distance_bias:
             specs += [TensorSpec("r1", (self.num_heads,), "positive"), TensorSpec("r2", (self.num_heads,), "positive")]
         specs += [TensorSpec("o", (h, self.num_heads * self.value_dim)), TensorSpec("o.b", (h,), "bias")]

@@ -19,21 +19,27 @@ from .base import Norm, PendingUpdate, TensorSpec, register_norm
 class RMSNorm(Norm):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
-    def __init__(self, dim: int, eps: float, groups: int = 1, name: str = "weight"):
-        """``name``: what the weight is called in a checkpoint, after the part's prefix."""
+    def __init__(self, dim: int, eps: float, groups: int = 1, name: str = "weight", optional: bool = False):
+        """``name``: what the weight is called in a checkpoint, after the part's prefix.
+        ``optional``: a norm that its block does not run (a layer without the sublayer it belongs
+        to); a checkpoint may hold its weight or not."""
         self.dim = int(dim)
         self.eps = float(eps)
         self.groups = int(groups)
         if self.groups < 1 or self.dim % self.groups:
             raise ValueError(f"a norm over {self.dim} channels cannot be cut into {groups} equal groups")
         self.name = name
+        self.optional = bool(optional)
         self.weight = None
 
     def tensor_specs(self):
-        return (TensorSpec(self.name, (self.dim,), init="norm"),)
+        return (TensorSpec(self.name, (self.dim,), init="norm", optional=self.optional),)
 
     def load(self, tensors, device, dtype):
-        self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
+        if self.name in tensors:
+            self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
+        elif not self.optional:
+            raise KeyError(self.name)
 
     def forward(self, ctx, x, delta, rows=None, defer=False):
         """``defer``: the caller's consumer can normalise inside its own kernel; when nothing

@@ -42,7 +42,8 @@ def test_every_size_comes_from_the_file():
     assert (mixers[3].window, mixers[3].keep_first, mixers[3].num_kv_heads) == (None, 0, 4)
     assert (mixers[0].width, mixers[0].blocks, mixers[0].conv, mixers[4].conv) == (64, 4, 3, 2)
     ffns = [b.feed_forward for b in model.blocks]
-    assert ffns[1] is None and ffns[4] is None and len(model.blocks[1].norms) == 2 and len(model.blocks[0].norms) == 4
+    assert ffns[1] is None and ffns[4] is None and [n.optional for n in model.blocks[1].norms] == [False, False, True, True]
+    assert not any(n.optional for n in model.blocks[0].norms)
     assert (ffns[0].experts, ffns[0].top, ffns[0].shared_size, ffns[2].shared_size, ffns[3].top) == (6, 2, 56, None, 1)
     assert all(n.groups == 3 and n.eps == 1e-5 for b in model.blocks for n in b.norms)
     needs = model.stop_needs()
@@ -55,8 +56,10 @@ def test_tensor_names_and_shapes():
     assert names["embed"] == (211, 96) and names["pos"] == (512, 96) and names["embed.norm"] == (96,)
     assert names["l0.mix.ra"] == (4, 16, 16) and names["l0.mix.conv"] == (64, 3) and names["l0.mix.o"] == (96, 64)
     assert names["l1.mix.q"] == (192, 96) and names["l1.mix.v"] == (32, 96) and names["l1.mix.o"] == (96, 96)
-    assert names["l1.mix.vmix"] == () and names["l1.mix.r1"] == (6,) and "l3.mix.vmix" not in names
-    assert "l1.norm2" not in names and "l1.mlp.router" not in names and names["l0.norm2b"] == (96,)
+    specs = build(R1).expected_tensors()
+    assert names["l1.mix.vmix"] == () and names["l1.mix.r1"] == (6,) and specs["l3.mix.vmix"].optional and not specs["l1.mix.vmix"].optional
+    assert specs["l1.norm2"].optional and specs["l4.norm2b"].optional and not specs["l0.norm2"].optional     # no feed-forward: never run
+    assert "l1.mlp.router" not in names and names["l0.norm2b"] == (96,)
     assert names["l0.mlp.e5.down"] == (96, 40) and names["l0.mlp.shared.sg"] == (1, 96) and "l2.mlp.shared.gate" not in names
     assert names["final.norm"] == (96,) and names["head"] == (211, 96)
 
@@ -84,7 +87,7 @@ def test_config_errors_name_the_key():
 def test_random_model_folder_loads_by_name(tmp_path):
     folder = write_random_model(str(tmp_path / "m"), R2, seed=3, prefix="")
     tensors = read_safetensors(os.path.join(folder, "model.safetensors"))
-    assert set(tensors) == set(build(R2).expected_tensors())
+    assert set(tensors) == {n for n, ts in build(R2).expected_tensors().items() if not ts.optional}
     assert (tensors["l0.mix.r2"] > 0).all() and 0 < float(tensors["l0.mix.r1"].min())
     with open(os.path.join(folder, "config.json")) as fh:
         assert json.load(fh)["architecture"] == "Rirulix"
@@ -101,7 +104,7 @@ def test_command_line_writes_a_folder_that_the_loader_accepts(tmp_path):
     assert main(["random-model", "--config", str(config), "--out", str(tmp_path / "m"), "--seed", "5", "--storage-dtype", "bfloat16"]) == 0
     model = build(R3)
     names = set(read_safetensors(str(tmp_path / "m" / "model.safetensors")))
-    assert {canonical_name(n, model.spec)[0] for n in names} == set(model.expected_tensors()) == names
+    assert {canonical_name(n, model.spec)[0] for n in names} == {n for n, ts in model.expected_tensors().items() if not ts.optional} == names
 
 
 def test_kept_first_pages_stay_while_the_window_releases():
