@@ -337,26 +337,29 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
     const unsigned char* Ws1 = Ws0 + W_BYTES;
 #pragma unroll
     for (int kk = 0; kk < BK / 16; ++kk) {
-      unsigned a[MI][4];
+      // all fragments of the step first, then all its products: a product does not wait for the load just before it
+      unsigned a[MI][4], b0[NJ / 2][4], b1[GATE_UP ? NJ / 2 : 1][4];
 #pragma unroll
       for (int i = 0; i < MI; ++i) ldmatrix_x4(a[i], st + (row_base + i * 16 + (lane & 15)) * P + (kk * 16 + 8 * (lane >> 4)) * 2);
 #pragma unroll
       for (int jp = 0; jp < NJ / 2; ++jp) {
         // two 8-column blocks at a time: (columns 0-7, k 0-7), (0-7, k 8-15), (8-15, k 0-7), (8-15, k 8-15)
         const int off = (col_base + jp * 16 + (lane & 7) + 8 * (lane >> 4)) * P + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2;
-        unsigned b[4];
-        ldmatrix_x4(b, Ws0 + off);
+        ldmatrix_x4(b0[jp], Ws0 + off);
+        if (GATE_UP) ldmatrix_x4(b1[jp], Ws1 + off);
+      }
+#pragma unroll
+      for (int jp = 0; jp < NJ / 2; ++jp) {
 #pragma unroll
         for (int i = 0; i < MI; ++i) {
-          mma_bf16(acc0[i][2 * jp], a[i], b[0], b[1]);
-          mma_bf16(acc0[i][2 * jp + 1], a[i], b[2], b[3]);
+          mma_bf16(acc0[i][2 * jp], a[i], b0[jp][0], b0[jp][1]);
+          mma_bf16(acc0[i][2 * jp + 1], a[i], b0[jp][2], b0[jp][3]);
         }
         if (GATE_UP) {
-          ldmatrix_x4(b, Ws1 + off);
 #pragma unroll
           for (int i = 0; i < MI; ++i) {
-            mma_bf16(acc1[i][2 * jp], a[i], b[0], b[1]);
-            mma_bf16(acc1[i][2 * jp + 1], a[i], b[2], b[3]);
+            mma_bf16(acc1[i][2 * jp], a[i], b1[jp][0], b1[jp][1]);
+            mma_bf16(acc1[i][2 * jp + 1], a[i], b1[jp][2], b1[jp][3]);
           }
         }
       }
