@@ -202,7 +202,8 @@ class CacheManager:
                     table.extend([-1] * (last - n - len(table)))
                     req.released[g.index] = len(table)
                 table.extend(g.pool.allocate(n))
-        req.reach = min(len(t) for t in req.tables) * self.page_size
+        # a model without any paged layer (recurrent mixers only) has nothing to reach for
+        req.reach = min((len(t) for t in req.tables), default=0) * self.page_size if self.groups else upto
 
     def advance(self, req: RequestCache, n_tokens: int) -> None:
         """``n_tokens`` more tokens are in the cache; pages wholly behind a window go back."""

@@ -526,6 +526,9 @@ static int moe_grouped_fma(const void* A, const void* W0, const void* W1, void* 
   } else if (tile == 64) {
     launch(moe_grouped_fma_kernel<T, GATE_UP, 64, 64, 16, 4, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
            (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
+  } else if (tile == 128) {     // the rows were laid out for the tensor-core product, which then did not take the operands
+    launch(moe_grouped_fma_kernel<T, GATE_UP, 128, 64, 16, 8, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
+           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
   } else {
     return (int)cudaErrorInvalidValue;
   }

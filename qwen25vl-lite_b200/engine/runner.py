@@ -566,7 +566,7 @@ class ModelRunner:
             q_start_pos=d(qs_s), slot_ids=d(sl_s), logit_rows=d(rows_s) if M else None,
             logits_every_row=(M == N == S and all(list(e.want) == [0] for e in entries)),
             max_q_len=max(q_lens),
-            max_kv_len=(max(widths) * ps if graph_key else max(s + n for s, n in zip(starts, q_lens))),
+            max_kv_len=(max(widths, default=1) * ps if graph_key else max(s + n for s, n in zip(starts, q_lens))),
             group_kv_slot=[d(s_) for s_ in g_slot_s],
             group_block_table=[d(s_, (S, w)) for s_, w in zip(g_tab_s, widths)],
             cache=self.cache,

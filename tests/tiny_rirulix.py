@@ -1,7 +1,7 @@
 """Tiny configurations of the Rirulix design for the tests, and the helper that writes them as model
 folders with random weights.
 
-The three differ in every size and option: widths, vocabularies, norm groups (1, 3, 4), layer
+The four differ in every size and option: widths, vocabularies, norm groups (1, 3, 4), layer
 orders, head counts and groupings (grouped, one kv head, as many kv heads as query heads), key and
 value sizes (equal and not), windows (none, shorter than a page, across pages) with 0 to 5 kept
 first tokens, value mixing on some layers or none, experts and choices per token (1 to 3), a shared
@@ -67,7 +67,15 @@ R3 = _config(160, 256, 1024, 4, 1e-6, [
     {"type": "attention", "mixer": _attn(6, 2, 64, 64, 0.11, 200, 7, True), "mlp": _moe(8, 1, 72, 1.75, (88, 1.25))},
 ])
 
-TINY = {"R1": (R1, 11, 16), "R2": (R2, 12, 8), "R3": (R3, 13, 16)}      # config, weight seed, page size
+# 3 layers of the recurrence alone: a model without a single cached key (no page is ever taken); every
+# expert is used by every token, so bfloat16 has no choice to flip.
+R4 = _config(120, 80, 400, 5, 1e-6, [
+    {"type": "rglru", "mixer": {"width": 48, "blocks": 3, "conv": 2}, "mlp": _moe(3, 3, 20, 1.5, (12, 0.5))},
+    {"type": "rglru", "mixer": {"width": 112, "blocks": 1, "conv": 5}, "mlp": None},
+    {"type": "rglru", "mixer": {"width": 80, "blocks": 5, "conv": 1}, "mlp": _moe(2, 2, 36, 2.5)},
+])
+
+TINY = {"R1": (R1, 11, 16), "R2": (R2, 12, 8), "R3": (R3, 13, 16), "R4": (R4, 14, 16)}      # config, weight seed, page size
 
 GAIN = 5.0       # what the matrices of the layers are multiplied by
 
