@@ -148,10 +148,12 @@ def test_recurrence_in_portions_with_state(dtype, width, blocks, taps):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,experts,top,hidden,ff", [(1, 4, 1, 64, 24), (7, 6, 2, 96, 40), (150, 5, 3, 128, 48), (300, 8, 1, 352, 72),
-                                                     (700, 4, 1, 72, 40), (33, 3, 2, 100, 30), (600, 2, 1, 44, 20)])
+                                                     (700, 4, 1, 72, 40), (33, 3, 2, 100, 30), (600, 2, 1, 44, 20),
+                                                     (1300, 4, 1, 72, 40), (1100, 16, 2, 64, 24)])
 def test_routed_experts(dtype, n, experts, top, hidden, ff):
-    """From one token to hundreds per expert (row tiles of 16, 64 and 128), one to three choices, and
-    sizes that the tensor-core product does not take (a width that is no multiple of 8)."""
+    """From one token to hundreds per expert (row tiles of 16, 64 and 128), one to three choices, sizes
+    that the tensor-core product does not take (a width that is no multiple of 8), and steps on both
+    sides of the number of pairs up to which one block sorts them."""
     from qwen25vl_lite.parts.feed_forward import RoutedGLU
 
     g = torch.Generator(device=DEV).manual_seed(5)
