@@ -152,8 +152,8 @@ def test_recurrence_in_portions_with_state(dtype, width, blocks, taps):
                                                      (1300, 4, 1, 72, 40), (1100, 16, 2, 64, 24)])
 def test_routed_experts(dtype, n, experts, top, hidden, ff):
     """From one token to hundreds per expert (row tiles of 16, 64 and 128), one to three choices, sizes
-    that the tensor-core product does not take (a width that is no multiple of 8), and steps on both
-    sides of the number of pairs up to which one block sorts them."""
+    that the tensor-core product does not take (a width that is no multiple of 8), and steps of more
+    than a thousand pairs."""
     from qwen25vl_lite.parts.feed_forward import RoutedGLU
 
     g = torch.Generator(device=DEV).manual_seed(5)
