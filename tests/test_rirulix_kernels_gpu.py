@@ -101,7 +101,7 @@ def recurrence_reference(yx, width, conv_w, conv_b, ra, ra_b, ri, ri_b, lam, gai
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,blocks,taps", [(64, 4, 3), (176, 1, 2), (96, 3, 1), (256, 2, 4)])
+@pytest.mark.parametrize("width,blocks,taps", [(64, 4, 3), (176, 1, 2), (96, 3, 1), (256, 2, 4), (66, 3, 2)])
 def test_recurrence_in_portions_with_state(dtype, width, blocks, taps):
     """Two requests of unequal length in three steps (portions of 1, 2 and many tokens, the second
     request absent from the middle step), in slots 2 and 0 of three: the state carries S and the
