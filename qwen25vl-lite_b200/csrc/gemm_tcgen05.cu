@@ -110,7 +110,12 @@ template <int EPI>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
-                    int bn, int n_stages, int* __restrict__ err) {
+                    int bn, int n_stages, int* __restrict__ err, const int* __restrict__ plan, int experts) {
+  // plan != nullptr: a grouped product.  The rows of x are sorted by expert in tiles of T5_BM rows;
+  // plan[0] says how many tiles there are and plan[2 + experts + t] which expert tile t belongs to
+  // (a kernel before this one wrote them); W holds the experts' matrices one after the other,
+  // [experts * N, K], and row tile t multiplies with rows expert * N + n0 ... of it.  Feature tiles
+  // that reach past an expert's N rows read the next expert's and are not stored.
   const int T5_BN = bn, T5_STAGES = n_stages, T5_STAGE_BYTES = T5_A_BYTES + bn * T5_BK * 2;
   extern __shared__ __align__(1024) unsigned char t5_smem[];
   // the dynamic shared memory starts with the stages (1024-byte aligned for the swizzle), the barriers follow
@@ -118,8 +123,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   T5Shared* sh = reinterpret_cast<T5Shared*>(stages + T5_STAGES * T5_STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_blocks = (M + T5_BM - 1) / T5_BM, n_blocks = (N + T5_BN - 1) / T5_BN;
-  const int n_tiles = m_blocks * n_blocks;
+  int m_blocks = (M + T5_BM - 1) / T5_BM;
+  const int n_blocks = (N + T5_BN - 1) / T5_BN;
   const int k_blocks = (K + T5_BK - 1) / T5_BK;
 
   pdl_trigger();
@@ -138,6 +143,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   // memory is asked for only after that kernel has finished: a CTA that held columns while it waited
   // could starve a CTA of the earlier kernel on the same SM that still has to allocate its own.
   pdl_wait();
+  if (plan) m_blocks = min(m_blocks, max(plan[0], 0));       // every thread reads the same count: the roles walk the same tiles
+  const int n_tiles = m_blocks * n_blocks;
   if (warp == 1) {   // tensor memory: two accumulators of up to 256 columns (the CTA has its SM to itself)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "n"(2 * T5_MAX_BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -154,6 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       int it = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int m0 = (tile % m_blocks) * T5_BM, n0 = (tile / m_blocks) * T5_BN;
+        const int w_row = plan ? plan[2 + experts + tile % m_blocks] * N + n0 : n0;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % T5_STAGES;
           if (it >= T5_STAGES && ok) {
@@ -163,7 +171,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           unsigned char* st = stages + (size_t)s * T5_STAGE_BYTES;
           mbar_expect_tx(sh->full + s, (unsigned)T5_STAGE_BYTES);
           t5_tma_load(st, &map_x, kb * T5_BK, m0, sh->full + s);
-          t5_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, n0, sh->full + s);
+          t5_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, w_row, sh->full + s);
         }
       }
     }
@@ -498,7 +506,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 
 template <int EPI>
 static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out, int ldo, int M, int N, int K,
-                     int bn, int* err, cudaStream_t s) {
+                     int bn, int* err, cudaStream_t s, const int* plan = nullptr, int experts = 0) {
   const int stages = t5_stages(bn);
   // the kernel may take the most any width needs: the attribute is set once per kernel, not per width
   const size_t most = (size_t)200 * 1024 + 1024 + sizeof(T5Shared);
@@ -509,7 +517,7 @@ static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* 
   const int sms = device_sm_count();
   if (sms <= 0) return (int)cudaErrorInvalidDevice;
   launch(gemm_tcgen05_kernel<EPI>, dim3(tiles < sms ? tiles : sms), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K,
-         bn, stages, err);
+         bn, stages, err, plan, experts);
   return launch_status();
 }
 
@@ -605,4 +613,24 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
     default: return (int)cudaErrorInvalidValue;
   }
 #undef T5_CASE
+}
+
+// The grouped product: x [M, K] are rows sorted by expert in tiles of 128 (M the most rows there can be),
+// W [experts, N, K] the experts' matrices, plan as the kernel says (on the device).  out [M, N]:
+// bfloat16 (epi 0) or float (epi 2).  The tiles are counted on the device, so nothing is read back.
+Q25_EXPORT int q25_gemm_tcgen05_grouped_bf16(const void* W, const void* X, int ldx, void* out, int ldo, int M, int N, int K,
+                                             int experts, const int* plan, int epi, int* err, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err || !plan || experts <= 0 || M % T5_BM)
+    return (int)cudaErrorInvalidValue;
+  CUtensorMap mx, mw;
+  int r = make_map(&mx, X, M, K, ldx, T5_BM);
+  if (r) return r;
+  const int bn = pick_bn(M > T5_BM ? M : T5_BM + 1, N);
+  r = make_map(&mw, W, experts * N, K, K, bn);
+  if (r) return r;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (epi == T5_STORE) return launch_t5<T5_STORE>(mx, mw, nullptr, out, ldo, M, N, K, bn, err, s, plan, experts);
+  if (epi == T5_F32) return launch_t5<T5_F32>(mx, mw, nullptr, out, ldo, M, N, K, bn, err, s, plan, experts);
+  return (int)cudaErrorInvalidValue;
 }

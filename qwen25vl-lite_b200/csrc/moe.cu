@@ -149,7 +149,7 @@ template <typename T, bool GATE_UP, int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 moe_grouped_fma_kernel(const T* __restrict__ A, const T* __restrict__ W0, const T* __restrict__ W1, void* __restrict__ out_,
                        const int* __restrict__ plan, const int* __restrict__ row_pair, const float* __restrict__ topk_w,
-                       int experts, int top, int N, int K, float limit, float alpha) {
+                       int experts, int top, int N, int K, long long w_stride, float limit, float alpha) {
   pdl_trigger();
   pdl_wait();
   constexpr int THREADS = (BM / TM) * (BN / TN);
@@ -174,8 +174,8 @@ moe_grouped_fma_kernel(const T* __restrict__ A, const T* __restrict__ W0, const 
   }
   __syncthreads();
   const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
-  const T* w0 = W0 + (size_t)e * N * K;
-  const T* w1 = GATE_UP ? W1 + (size_t)e * N * K : nullptr;
+  const T* w0 = W0 + (size_t)e * w_stride;              // w_stride: values from one expert's matrix to the next one's
+  const T* w1 = GATE_UP ? W1 + (size_t)e * w_stride : nullptr;
   float acc0[TM][TN], acc1[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
@@ -272,8 +272,8 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restr
 template <bool GATE_UP, int BM, int WARPS_M, int STAGES>
 __global__ void __launch_bounds__(128)
 moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, const bf16* __restrict__ W1, void* __restrict__ out_,
-                       const int* __restrict__ plan, const int* __restrict__ row_pair, int experts, int N, int K, float limit,
-                       float alpha) {
+                       const int* __restrict__ plan, const int* __restrict__ row_pair, int experts, int N, int K, long long w_stride,
+                       float limit, float alpha) {
   pdl_trigger();
   pdl_wait();
   constexpr int BN = 64, BK = 64, P = BK * 2 + 16;            // pitch in bytes: an odd number of 16-byte chunks
@@ -289,8 +289,8 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int m0 = tile * BM, n0 = blockIdx.x * BN;
   for (int r = threadIdx.x; r < BM; r += 128) src_row[r] = row_pair[m0 + r];
-  const bf16* w0 = W0 + (size_t)e * N * K;
-  const bf16* w1 = GATE_UP ? W1 + (size_t)e * N * K : nullptr;
+  const bf16* w0 = W0 + (size_t)e * w_stride;
+  const bf16* w1 = GATE_UP ? W1 + (size_t)e * w_stride : nullptr;
   const bf16* a0 = A + (size_t)m0 * K;
   const int nk = (K + BK - 1) / BK;
   auto load = [&](int kt) {
@@ -487,26 +487,26 @@ Q25_EXPORT int q25_moe_sort(const int* topk_idx, const int* counts, int* cursor,
 
 template <bool GATE_UP, int BM, int WARPS_M, int STAGES>
 static int moe_grouped_mma_shape(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
-                                 int tiles, int experts, int N, int K, float limit, float alpha, cudaStream_t s) {
+                                 int tiles, int experts, int N, int K, long long w_stride, float limit, float alpha, cudaStream_t s) {
   constexpr int SMEM = STAGES * (BM + (GATE_UP ? 128 : 64)) * (64 * 2 + 16);
   const cudaError_t e = cudaFuncSetAttribute(moe_grouped_mma_kernel<GATE_UP, BM, WARPS_M, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   if (e != cudaSuccess) return (int)e;
   launch(moe_grouped_mma_kernel<GATE_UP, BM, WARPS_M, STAGES>, dim3((N + 63) / 64, tiles), dim3(128), SMEM, s, (const bf16*)A, (const bf16*)W0,
-         (const bf16*)W1, out, plan, row_pair, experts, N, K, limit, alpha);
+         (const bf16*)W1, out, plan, row_pair, experts, N, K, w_stride, limit, alpha);
   return launch_status();
 }
 
 // A: the rows in the sorted order, [rows, K] bfloat16.
 template <bool GATE_UP>
 static int moe_grouped_mma(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
-                           int n_pairs, int experts, int N, int K, float limit, float alpha, int tile, void* stream) {
+                           int n_pairs, int experts, int N, int K, long long w_stride, float limit, float alpha, int tile, void* stream) {
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
   cudaStream_t s = (cudaStream_t)stream;
-  if (tile == 16) return moe_grouped_mma_shape<GATE_UP, 16, 1, 4>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
+  if (tile == 16) return moe_grouped_mma_shape<GATE_UP, 16, 1, 4>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, s);
   // two stages for the large tiles: three or four CTAs then share an SM (12 to 16 warps), which hides the fixed latencies between
   // a fragment's load and its products better than a third stage does (gate and up at 4,096 rows: 268 us with three stages)
-  if (tile == 64) return moe_grouped_mma_shape<GATE_UP, 64, 2, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
-  if (tile == 128) return moe_grouped_mma_shape<GATE_UP, 128, 4, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, limit, alpha, s);
+  if (tile == 64) return moe_grouped_mma_shape<GATE_UP, 64, 2, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, s);
+  if (tile == 128) return moe_grouped_mma_shape<GATE_UP, 128, 4, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, s);
   return (int)cudaErrorInvalidValue;
 }
 
@@ -516,53 +516,68 @@ static bool moe_mma_takes(const void* A, const void* W0, const void* W1, const v
 
 template <typename T, bool GATE_UP>
 static int moe_grouped_fma(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
-                           const float* topk_w, int n_pairs, int experts, int top, int N, int K, float limit, float alpha, int tile,
-                           void* stream) {
+                           const float* topk_w, int n_pairs, int experts, int top, int N, int K, long long w_stride, float limit,
+                           float alpha, int tile, void* stream) {
   if (n_pairs <= 0) return 0;
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
   if (tile == 16) {
     launch(moe_grouped_fma_kernel<T, GATE_UP, 16, 64, 16, 1, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
-           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
+           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha);
   } else if (tile == 64) {
     launch(moe_grouped_fma_kernel<T, GATE_UP, 64, 64, 16, 4, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
-           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
+           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha);
   } else if (tile == 128) {     // the rows were laid out for the tensor-core product, which then did not take the operands
     launch(moe_grouped_fma_kernel<T, GATE_UP, 128, 64, 16, 8, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
-           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, limit, alpha);
+           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha);
   } else {
     return (int)cudaErrorInvalidValue;
   }
   return launch_status();
 }
 
-// sorted: [max rows, hidden] of scratch in the activation dtype for the rows in the sorted order
-// (bfloat16: the tensor-core product reads them; nullptr or float: the product gathers by itself).
-Q25_EXPORT int q25_moe_gate_up_f32(const void* h, const void* wg, const void* wu, void* act, const int* plan, const int* row_pair,
+// wgu: the experts' gate and up matrices, [experts, 2 * ff, hidden]: an expert's ff gate rows, then its
+// ff up rows.  sorted: [max rows, hidden] of scratch in the activation dtype for the rows in the sorted
+// order (bfloat16: the tensor-core product reads them; nullptr or float: the product gathers by itself).
+Q25_EXPORT int q25_moe_gate_up_f32(const void* h, const void* wgu, void* act, const int* plan, const int* row_pair,
                                    const float* topk_w, int n_pairs, int experts, int top, int ff, int hidden, float limit,
                                    float alpha, int tile, void* sorted, void* s) {
-  return moe_grouped_fma<float, true>(h, wg, wu, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden, limit, alpha, tile, s);
+  const float* w = (const float*)wgu;
+  return moe_grouped_fma<float, true>(h, w, w + (size_t)ff * hidden, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden,
+                                      2LL * ff * hidden, limit, alpha, tile, s);
 }
-Q25_EXPORT int q25_moe_gate_up_bf16(const void* h, const void* wg, const void* wu, void* act, const int* plan, const int* row_pair,
+Q25_EXPORT int q25_moe_gather_bf16(const void* h, const int* row_pair, const float* topk_w, void* sorted, int rows, int top, int hidden,
+                                   void* s) {
+  if (rows <= 0) return 0;
+  if (hidden % 8 || (((uintptr_t)h | (uintptr_t)sorted) & 15)) return (int)cudaErrorInvalidValue;
+  launch(moe_gather_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)s, (const bf16*)h, row_pair, topk_w, (bf16*)sorted, top, hidden);
+  return launch_status();
+}
+Q25_EXPORT int q25_moe_gate_up_bf16(const void* h, const void* wgu, void* act, const int* plan, const int* row_pair,
                                     const float* topk_w, int n_pairs, int experts, int top, int ff, int hidden, float limit,
                                     float alpha, int tile, void* sorted, void* s) {
   if (n_pairs <= 0) return 0;
-  if (sorted && moe_mma_takes(h, wg, wu, sorted, hidden)) {
+  const bf16* w = (const bf16*)wgu;
+  const bf16* wu = w + (size_t)ff * hidden;
+  if (sorted && moe_mma_takes(h, w, wu, sorted, hidden)) {
     launch(moe_gather_kernel, dim3(q25_moe_max_rows(n_pairs, experts, tile)), dim3(128), 0, (cudaStream_t)s, (const bf16*)h, row_pair, topk_w,
            (bf16*)sorted, top, hidden);
-    return moe_grouped_mma<true>(sorted, wg, wu, act, plan, row_pair, n_pairs, experts, ff, hidden, limit, alpha, tile, s);
+    return moe_grouped_mma<true>(sorted, w, wu, act, plan, row_pair, n_pairs, experts, ff, hidden, 2LL * ff * hidden, limit, alpha, tile, s);
   }
-  return moe_grouped_fma<bf16, true>(h, wg, wu, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden, limit, alpha, tile, s);
+  return moe_grouped_fma<bf16, true>(h, w, wu, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden, 2LL * ff * hidden, limit, alpha,
+                                     tile, s);
 }
 Q25_EXPORT int q25_moe_down_f32(const void* act, const void* wd, void* y, const int* plan, const int* row_pair, int n_pairs,
                                 int experts, int top, int hidden, int ff, int tile, void* s) {
-  return moe_grouped_fma<float, false>(act, wd, nullptr, y, plan, row_pair, nullptr, n_pairs, experts, top, hidden, ff, 0.f, 0.f, tile, s);
+  return moe_grouped_fma<float, false>(act, wd, nullptr, y, plan, row_pair, nullptr, n_pairs, experts, top, hidden, ff, (long long)hidden * ff,
+                                       0.f, 0.f, tile, s);
 }
 Q25_EXPORT int q25_moe_down_bf16(const void* act, const void* wd, void* y, const int* plan, const int* row_pair, int n_pairs,
                                  int experts, int top, int hidden, int ff, int tile, void* s) {
   if (n_pairs <= 0) return 0;
   if (moe_mma_takes(act, wd, nullptr, nullptr, ff))
-    return moe_grouped_mma<false>(act, wd, nullptr, y, plan, row_pair, n_pairs, experts, hidden, ff, 0.f, 0.f, tile, s);
-  return moe_grouped_fma<bf16, false>(act, wd, nullptr, y, plan, row_pair, nullptr, n_pairs, experts, top, hidden, ff, 0.f, 0.f, tile, s);
+    return moe_grouped_mma<false>(act, wd, nullptr, y, plan, row_pair, n_pairs, experts, hidden, ff, (long long)hidden * ff, 0.f, 0.f, tile, s);
+  return moe_grouped_fma<bf16, false>(act, wd, nullptr, y, plan, row_pair, nullptr, n_pairs, experts, top, hidden, ff, (long long)hidden * ff,
+                                      0.f, 0.f, tile, s);
 }
 
 template <typename T>

@@ -28,16 +28,17 @@ NVCC_FLAGS = [
 ]
 
 # library name -> sources.  "core" holds every kernel of the 32-bit path and the generic
-# bfloat16 ones; "chain" the weight-streaming product of bfloat16 decode steps; "bf16" the
-# tensor-core attention and the tcgen05 product that only the serving path of rotary softmax
-# attention loads; "recurrent", "biased" and "routed" the kernels of the gated linear recurrence,
+# bfloat16 ones; "chain" the weight-streaming product of bfloat16 decode steps; "tcgen05" the
+# tcgen05 product (dense, and grouped by expert); "bf16" the tensor-core attention that only the
+# serving path of rotary softmax attention loads; "recurrent", "biased" and "routed" the kernels of the gated linear recurrence,
 # of attention with a distance bias and kept first tokens, and of the routed feed-forward.  A
 # library is compiled when a model first asks for one of its kernels, so a run compiles only what
 # its model and dtype need.
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu"],
     "chain": ["gemm_chain.cu"],
-    "bf16": ["attention_mma.cu", "attention_tcgen05.cu", "gemm_tcgen05.cu"],
+    "tcgen05": ["gemm_tcgen05.cu"],
+    "bf16": ["attention_mma.cu", "attention_tcgen05.cu"],
     "recurrent": ["recurrent.cu"],
     "biased": ["attention_biased.cu"],
     "routed": ["moe.cu"],

@@ -34,7 +34,7 @@ _SIGNATURES = {
     "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "q25_kv_store_mix": [_P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
+    "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "q25_moe_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
@@ -72,7 +72,7 @@ def load_library(name: str = "core") -> ctypes.CDLL:
 # which library holds a symbol, by the symbol's beginning (everything else is in "core"); a
 # library is compiled and loaded when one of its kernels is first asked for
 _SYMBOL_LIBRARY = (("q25_gemm_chain", "chain"), ("q25_attention_decode", "bf16"), ("q25_attention_prefill", "bf16"),
-                   ("q25_gemm_tcgen05", "bf16"), ("q25_rope_angles", "bf16"), ("q25_rglru", "recurrent"),
+                   ("q25_gemm_tcgen05", "tcgen05"), ("q25_rope_angles", "bf16"), ("q25_rglru", "recurrent"),
                    ("q25_biased_attention", "biased"), ("q25_kv_store_mix", "biased"), ("q25_moe", "routed"))
 
 
@@ -812,19 +812,50 @@ def moe_sort(topk_idx: torch.Tensor, counts: torch.Tensor, cursor: torch.Tensor,
     count_replayed(1)                          # two kernels in one call
 
 
-def moe_gate_up(h: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, act: torch.Tensor, plan: torch.Tensor,
-                row_pair: torch.Tensor, topk_w: torch.Tensor, top: int, limit: float, alpha: float, tile: int) -> None:
-    """act[row] = glu(expert of the row's tile applied to weight * h[token of the row]) for the sorted rows."""
-    experts, ff, hidden = w_gate.shape
+def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, plan: torch.Tensor, row_pair: torch.Tensor,
+                topk_w: torch.Tensor, top: int, limit: float, alpha: float, tile: int) -> None:
+    """act[row] = glu(expert of the row's tile applied to weight * h[token of the row]) for the sorted
+    rows.  ``w_gate_up``: [experts, 2 * ff, hidden], an expert's gate rows and then its up rows."""
+    experts, ff2, hidden = w_gate_up.shape
     _dev(h, act.dtype, "moe_gate_up input")
-    _dev(w_gate, h.dtype, "moe_gate_up gate"); _dev(w_up, h.dtype, "moe_gate_up up"); _dev(act, h.dtype, "moe_gate_up act")
+    _dev(w_gate_up, h.dtype, "moe_gate_up weights"); _dev(act, h.dtype, "moe_gate_up act")
     # bfloat16: the rows are first written out in the sorted order, weighted, for the tensor-core product
     sorted_rows = torch.empty((act.shape[0], hidden), dtype=h.dtype, device=h.device) if h.dtype == torch.bfloat16 else None
-    _check(_typed("q25_moe_gate_up", h.dtype)(h.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), act.data_ptr(), plan.data_ptr(),
-                                              row_pair.data_ptr(), topk_w.data_ptr(), topk_w.numel(), experts, int(top), ff, hidden,
+    _check(_typed("q25_moe_gate_up", h.dtype)(h.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), plan.data_ptr(),
+                                              row_pair.data_ptr(), topk_w.data_ptr(), topk_w.numel(), experts, int(top), ff2 // 2, hidden,
                                               float(limit), float(alpha), int(tile), _ptr(sorted_rows), _stream()), "moe_gate_up")
     if sorted_rows is not None:
         count_replayed(1)
+
+
+def moe_gather(h: torch.Tensor, row_pair: torch.Tensor, topk_w: torch.Tensor, top: int, sorted_rows: torch.Tensor) -> None:
+    """sorted_rows[row] = weight of the row's pair * h[token of the pair] (bfloat16), the input of the grouped products."""
+    _dev(h, torch.bfloat16, "moe_gather input"); _dev(sorted_rows, torch.bfloat16, "moe_gather rows")
+    _check(_fn("q25_moe_gather_bf16", [_P, _P, _P, _P, _I, _I, _I, _P])(
+        h.data_ptr(), row_pair.data_ptr(), topk_w.data_ptr(), sorted_rows.data_ptr(), sorted_rows.shape[0], int(top), h.shape[1],
+        _stream()), "moe_gather")
+
+
+GROUPED_TILE = 128              # rows of a tile of the tcgen05 grouped product
+
+
+def gemm_tcgen05_grouped_supports(x_dtype: torch.dtype, hidden: int, ff: int) -> bool:
+    """What the grouped tcgen05 product takes: bfloat16 rows whose pitch is a multiple of 16 bytes."""
+    return x_dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0
+
+
+def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: torch.Tensor) -> None:
+    """out[row] = x[row] . w[expert of the row's tile]^T on the tcgen05 tensor cores: ``x`` [rows, K] sorted by
+    expert in tiles of ``GROUPED_TILE`` rows (rows: the most there can be), ``w`` [experts, N, K], ``plan`` as
+    ``moe_sort`` leaves it on the device; ``out`` [rows, N] bfloat16 or float32."""
+    rows, k = x.shape
+    experts, n, k2 = w.shape
+    if (k2 != k or rows % GROUPED_TILE or out.shape != (rows, n) or out.dtype not in (torch.bfloat16, torch.float32)
+            or not gemm_tcgen05_supports(x, w.view(experts * n, k))):
+        raise KernelError(f"gemm_tcgen05_grouped: unsupported operands {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+    _check(_fn("q25_gemm_tcgen05_grouped_bf16", [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P])(
+        w.data_ptr(), x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), rows, n, k, experts, plan.data_ptr(),
+        SKINNY_F32 if out.dtype == torch.float32 else SKINNY_STORE, error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05_grouped")
 
 
 def moe_down(act: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor, plan: torch.Tensor, row_pair: torch.Tensor, n_pairs: int,

@@ -61,6 +61,9 @@ class SwiGLU(FeedForward):
         return self.down_proj(act, residual=residual)
 
 
+TCGEN05_MIN_WIDTH = 2048        # from this width on the grouped products of long steps run on tcgen05
+
+
 @register_feed_forward("routed_glu")
 class RoutedGLU(FeedForward):
     """A mixture of ``experts`` small gated feed-forwards of which each token uses ``top``, plus an
@@ -74,7 +77,8 @@ class RoutedGLU(FeedForward):
     by ``sigmoid(wsg . h)``, one number per token.
 
     The pairs of a step are sorted by expert on the device and two grouped products walk them
-    (``csrc/moe.cu``); the host reads nothing back, so a step of single tokens can be captured."""
+    (``csrc/moe.cu``; in long bfloat16 steps of wide models the grouped mode of ``csrc/gemm_tcgen05.cu``);
+    the host reads nothing back, so a step of single tokens can be captured."""
 
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
@@ -100,8 +104,10 @@ class RoutedGLU(FeedForward):
         return tuple(specs)
 
     def load(self, tensors, device, dtype):
-        stack = lambda what: torch.stack([tensors[f"e{e}.{what}"] for e in range(self.experts)]).to(device=device, dtype=dtype).contiguous()
-        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        # an expert's gate rows and then its up rows, expert after expert: the layout that one grouped product reads whole
+        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                      for e in range(self.experts)]).to(device=device, dtype=dtype).contiguous()
+        self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).to(device=device, dtype=dtype).contiguous()
         self.router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
         self.shared_gate = self.shared_gate_up = self.shared_down = None
         if self.shared_size:
@@ -114,8 +120,14 @@ class RoutedGLU(FeedForward):
         n, top, experts = h.shape[0], self.top, self.experts
         pairs = n * top
         # rows of a tile of the grouped products, from the step's shape alone: 16 while an expert gets 16
-        # rows on average (the product is then a stream of weights), 128 from 128 on (bfloat16)
-        tile = 16 if pairs <= 16 * experts else (128 if pairs >= 128 * experts and ctx.dtype == torch.bfloat16 else 64)
+        # rows on average (the product is then a stream of weights), 128 from an average of 128 on (when
+        # an expert gets 128: bfloat16, on tcgen05 when the sizes allow it, else mma.sync)
+        many = pairs >= 128 * experts and ctx.dtype == torch.bfloat16
+        # measured, a 2,048-token prompt of six layers: width 2,048: 4.73 ms with mma.sync, 3.67 ms with tcgen05; width
+        # 2,560: 6.59 and 5.70 ms; width 1,024 (a tile's walk over K is then short against its epilogue): 2.68 and 2.86 ms
+        tcgen05 = (many and self.hidden_size >= TCGEN05_MIN_WIDTH
+                   and kernels.gemm_tcgen05_grouped_supports(ctx.dtype, self.hidden_size, self.expert_size))
+        tile = 16 if pairs <= 16 * experts else (128 if many else 64)
         rows = kernels.moe_max_rows(pairs, experts, tile)
         dev = h.device
         shared = None
@@ -136,9 +148,19 @@ class RoutedGLU(FeedForward):
         kernels.moe_route(h, self.router, self.shared_gate, top, topk_idx, topk_w, sg, counts)
         kernels.moe_sort(topk_idx, counts, cursor, plan, row_pair, pair_row, experts, tile)
         act = torch.empty((rows, self.expert_size), dtype=ctx.dtype, device=dev)
-        kernels.moe_gate_up(h, self.w_gate, self.w_up, act, plan, row_pair, topk_w, top, self.limit, self.alpha, tile)
         y = torch.empty((rows, self.hidden_size), dtype=torch.float32, device=dev)
-        kernels.moe_down(act, self.w_down, y, plan, row_pair, pairs, top, tile)
+        if tcgen05:
+            # long steps: the sorted rows, weighted; gate and up of every expert as one grouped product on tcgen05
+            # (which finds its tiles in the plan on the device), the activation, and down the same way
+            sorted_rows = torch.empty((rows, self.hidden_size), dtype=ctx.dtype, device=dev)
+            kernels.moe_gather(h, row_pair, topk_w, top, sorted_rows)
+            gate_up = torch.empty((rows, 2 * self.expert_size), dtype=ctx.dtype, device=dev)
+            kernels.gemm_tcgen05_grouped(sorted_rows, self.w_gate_up, gate_up, plan)
+            kernels.glu_clamped(gate_up, act, self.limit, self.alpha)
+            kernels.gemm_tcgen05_grouped(act, self.w_down, y, plan)
+        else:
+            kernels.moe_gate_up(h, self.w_gate_up, act, plan, row_pair, topk_w, top, self.limit, self.alpha, tile)
+            kernels.moe_down(act, self.w_down, y, plan, row_pair, pairs, top, tile)
         out = torch.empty((n, self.hidden_size), dtype=ctx.dtype, device=dev)
         kernels.moe_combine(y, pair_row, sg, shared, out, top)
         return out

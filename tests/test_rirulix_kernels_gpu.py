@@ -150,12 +150,14 @@ def test_recurrence_in_portions_with_state(dtype, width, blocks, taps):
 @pytest.mark.parametrize("n,experts,top,hidden,ff", [(1, 4, 1, 64, 24), (7, 6, 2, 96, 40), (150, 5, 3, 128, 48), (300, 8, 1, 352, 72),
                                                      (700, 4, 1, 72, 40), (33, 3, 2, 100, 30), (600, 2, 1, 44, 20),
                                                      (1300, 4, 1, 72, 40), (1100, 16, 2, 64, 24)])
-def test_routed_experts(dtype, n, experts, top, hidden, ff):
+def test_routed_experts(dtype, n, experts, top, hidden, ff, monkeypatch):
     """From one token to hundreds per expert (row tiles of 16, 64 and 128), one to three choices, sizes
     that the tensor-core product does not take (a width that is no multiple of 8), and steps of more
-    than a thousand pairs."""
+    than a thousand pairs.  Long bfloat16 steps whose sizes allow it take the grouped tcgen05 product."""
+    from qwen25vl_lite.parts import feed_forward
     from qwen25vl_lite.parts.feed_forward import RoutedGLU
 
+    monkeypatch.setattr(feed_forward, "TCGEN05_MIN_WIDTH", 64)          # the tcgen05 grouped product at these small widths too
     g = torch.Generator(device=DEV).manual_seed(5)
     rnd = lambda *shape, scale=1.0: torch.randn(*shape, generator=g, device=DEV) * scale
     part = RoutedGLU(hidden, experts, top, ff, limit=1.5, shared_size=32, shared_limit=0.75)
