@@ -119,9 +119,9 @@ class RoutedGLU(FeedForward):
     def forward(self, ctx, h):
         n, top, experts = h.shape[0], self.top, self.experts
         pairs = n * top
-        # rows of a tile of the grouped products, from the step's shape alone: 16 while an expert gets 16
-        # rows on average (the product is then a stream of weights), 128 from an average of 128 on (when
-        # an expert gets 128: bfloat16, on tcgen05 when the sizes allow it, else mma.sync)
+        # rows of a tile of the grouped products, from the step's shape alone: 16 while an expert gets up to 16
+        # rows on average (the product is then a stream of weights), 64 beyond, and in bfloat16 128 once an
+        # expert gets 128 rows on average: on tcgen05 where the width and the sizes allow it, else mma.sync
         many = pairs >= 128 * experts and ctx.dtype == torch.bfloat16
         # measured, a 2,048-token prompt of six layers: width 2,048: 4.73 ms with mma.sync, 3.67 ms with tcgen05; width
         # 2,560: 6.59 and 5.70 ms; width 1,024 (a tile's walk over K is then short against its epilogue): 2.68 and 2.86 ms
