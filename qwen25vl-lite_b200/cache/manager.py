@@ -72,7 +72,8 @@ class CacheGroup:
         return -(-self.need.keep_first // self.page_size) if self.window is not None else 0
 
     def bytes_per_token(self, element_size: int) -> int:
-        return len(self.stops) * self.need.kv_heads * (self.need.head_dim + self.need.v_dim) * element_size
+        per_head = self.need.head_dim + (0 if self.need.value_in_key else self.need.v_dim)
+        return len(self.stops) * self.need.kv_heads * per_head * element_size
 
 
 @dataclass(eq=False)
@@ -140,7 +141,9 @@ class CacheManager:
     def allocate_device(self, device, dtype: torch.dtype) -> None:
         for g in self.groups:
             shape = (len(g.stops), self.num_pages, g.need.kv_heads, self.page_size)
-            if g.need.v_dim == g.need.head_dim:
+            if g.need.value_in_key:                  # a value is the beginning of its key row: one tensor serves both
+                g.k_pages = g.v_pages = torch.zeros((*shape, g.need.head_dim), dtype=dtype, device=device)
+            elif g.need.v_dim == g.need.head_dim:
                 both = torch.zeros((shape[0], 2, *shape[1:], g.need.head_dim), dtype=dtype, device=device)
                 g.k_pages, g.v_pages = both[:, 0], both[:, 1]
             else:
@@ -150,7 +153,8 @@ class CacheManager:
             self.states[i] = torch.zeros((self.max_requests, *need.shape), dtype=getattr(torch, need.dtype), device=device)
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for g in self.groups for t in (g.k_pages, g.v_pages) if t is not None)
+        return sum(t.numel() * t.element_size() for g in self.groups
+                   for t in ((g.k_pages,) if g.need.value_in_key else (g.k_pages, g.v_pages)) if t is not None)
 
     def stop_pages(self, stop: int) -> Tuple[CacheGroup, torch.Tensor, torch.Tensor]:
         gi, li = self.location[stop]

@@ -5,6 +5,8 @@
 //   score(i, j) = (q_i . k_j) * scale - r1[h] * ln(1 + r2[h] * (i - j))        (r1 == nullptr: no bias)
 //   query i sees key j when j <= i and (i - j < window or j < keep_first)       (window 0: all j <= i)
 //   o_i = softmax_j(score) v_j;  query head h reads kv head h / (nq / nkv)
+//   sink[h] (optional): a score without key or value that joins the softmax's denominator
+//   v_row (optional): values that lie inside the key rows (a latent cache): channels between value rows
 //
 // and the write of a step's keys and values into their pages, where the values may first be mixed
 // with those another layer computed for the same token: v <- (1 - mix) v + mix v_other.
@@ -24,7 +26,7 @@ __global__ void biased_attention_generic_kernel(
     const T* __restrict__ vpages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ token_seq, const int* __restrict__ cu_q, const int* __restrict__ q_start_pos,
     int n_tokens, int nq, int nkv, int dk, int dv, int page_size, int window, int keep_first, float scale,
-    const float* __restrict__ r1, const float* __restrict__ r2) {
+    const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink, int v_row) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char att_smem[];
@@ -67,7 +69,7 @@ __global__ void biased_attention_generic_kernel(
       if (valid) {
         const int page = table[key / page_size];
         const size_t row = ((size_t)page * nkv + kvh) * page_size + (key % page_size);
-        off = row * dv;
+        off = row * v_row;
         const T* kr = kpages + row * dk;
         float dot = 0.f;
         for (int c = 0; c < dk; ++c) dot = fmaf(qs[c], to_f32(kr[c]), dot);
@@ -97,6 +99,7 @@ __global__ void biased_attention_generic_kernel(
     }
   }
   T* o = out + (size_t)token * nq * dv + (size_t)head * dv;
+  if (sink) l += expf(sink[head] - m);                // a score without key or value: it only takes its share of the weight
   const float inv_l = 1.0f / l;
 #pragma unroll
   for (int i = 0; i < BATT_MAX_D / 32; ++i) {
@@ -139,8 +142,10 @@ template <typename T>
 static int biased_attention_generic(const void* qkv, int qkv_stride, void* out, const void* kpages, const void* vpages,
                                     const int* block_table, int table_width, const int* token_seq, const int* cu_q,
                                     const int* q_start_pos, int n_tokens, int nq, int nkv, int dk, int dv, int page_size,
-                                    int window, int keep_first, float scale, const float* r1, const float* r2, void* stream) {
+                                    int window, int keep_first, float scale, const float* r1, const float* r2, const float* sink,
+                                    int v_row, void* stream) {
   if (n_tokens <= 0) return 0;
+  if (v_row <= 0) v_row = dv;
   if (dk <= 0 || dv <= 0 || dv > BATT_MAX_D || dk > 4096 || nkv <= 0 || nq % nkv || window < 0 || keep_first < 0)
     return (int)cudaErrorInvalidValue;
   const long long items = (long long)n_tokens * nq;
@@ -152,7 +157,7 @@ static int biased_attention_generic(const void* qkv, int qkv_stride, void* out, 
   }
   launch(biased_attention_generic_kernel<T>, dim3(blocks), dim3(BATT_WARPS * 32), smem, (cudaStream_t)stream, (const T*)qkv,
          qkv_stride, (T*)out, (const T*)kpages, (const T*)vpages, block_table, table_width, token_seq, cu_q, q_start_pos, n_tokens,
-         nq, nkv, dk, dv, page_size, window, keep_first, scale, r1, r2);
+         nq, nkv, dk, dv, page_size, window, keep_first, scale, r1, r2, sink, v_row);
   return launch_status();
 }
 
@@ -166,16 +171,14 @@ static int kv_store_mix(void* qkv, int qkv_stride, const void* v_other, int ld_o
 }
 
 Q25_EXPORT int q25_biased_attention_generic_f32(const void* qkv, int qs, void* out, const void* kp, const void* vp, const int* bt,
-                                                int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk,
-                                                int dv, int ps, int window, int keep, float scale, const float* r1, const float* r2,
-                                                void* s) {
-  return biased_attention_generic<float>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, s);
+        int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
+        const float* r1, const float* r2, const float* sink, int v_row, void* s) {
+  return biased_attention_generic<float>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, s);
 }
 Q25_EXPORT int q25_biased_attention_generic_bf16(const void* qkv, int qs, void* out, const void* kp, const void* vp, const int* bt,
-                                                 int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk,
-                                                 int dv, int ps, int window, int keep, float scale, const float* r1, const float* r2,
-                                                 void* s) {
-  return biased_attention_generic<bf16>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, s);
+        int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
+        const float* r1, const float* r2, const float* sink, int v_row, void* s) {
+  return biased_attention_generic<bf16>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, s);
 }
 Q25_EXPORT int q25_kv_store_mix_f32(void* qkv, int qs, const void* vo, int ldo, float mix, void* kp, void* vp, const int* slot, int n,
                                     int nq, int nkv, int dk, int dv, int ps, void* s) {
@@ -221,6 +224,8 @@ struct BiasedArgs {
   float scale_log2;
   const float* r1;
   const float* r2;
+  const float* sink;   // per query head, a score without key or value that joins the denominator (nullptr: none)
+  int v_row;           // channels between two value rows of a page (DV, or the key row's when values lie inside the keys)
   int n_splits;
   float* part_o;   // [items, nq, splits, DV]
   float* part_ml;  // [items, nq, splits, 2]
@@ -260,7 +265,7 @@ __device__ __forceinline__ void biased_load_tile(unsigned char* ks, unsigned cha
   const int page = table[kc / a.page_size];
   const size_t row = ((size_t)page * a.nkv + kvh) * a.page_size + kc % a.page_size;
   const bf16* kr = a.kpages + row * DK;
-  const bf16* vr = a.vpages + row * DV;
+  const bf16* vr = a.vpages + row * a.v_row;
 #pragma unroll
   for (int i = 0; i < CK / TPK; ++i) {
     const int ch = part + i * TPK;
@@ -428,7 +433,11 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
       biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
     __syncthreads();
   }
-  const float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
+  float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
+  if (a.sink) {                                              // scores live in the base-2 domain
+    if (tok0 >= 0) l0 += exp2f(a.sink[h0] * 1.4426950408889634f - m[0]);
+    if (tok1 >= 0) l1 += exp2f(a.sink[h1] * 1.4426950408889634f - m[1]);
+  }
   const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
 #pragma unroll
   for (int nb = 0; nb < DV / 8; ++nb) {
@@ -524,6 +533,7 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
     }
     const int head = kvh * group + r;
     if (a.n_splits == 1) {
+      if (a.sink && mm != -INFINITY) sum += exp2f(a.sink[head] * 1.4426950408889634f - mm);
       a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
     } else {
       const size_t at = ((size_t)item * a.nq + head) * a.n_splits + split;
@@ -550,6 +560,7 @@ __global__ void biased_combine_kernel(BiasedArgs a) {
     sum = fmaf(a.part_ml[(base + s) * 2 + 1], f, sum);
     acc = fmaf(a.part_o[(base + s) * DV + c], f, acc);
   }
+  if (a.sink && mm != -INFINITY) sum += exp2f(a.sink[head] * 1.4426950408889634f - mm);
   a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
 }
 
@@ -591,14 +602,15 @@ Q25_EXPORT int q25_biased_attention_mma_supports(int dk, int dv) {
 Q25_EXPORT int q25_biased_attention_mma_bf16(const void* qkv, int qkv_stride, void* out, const void* kp, const void* vp, const int* bt,
                                              int tw, const int* cu, const int* sp, const int* tiles, int n_tiles, const int* items,
                                              int n_items, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
-                                             const float* r1, const float* r2, int n_splits, float* part_o, float* part_ml, void* stream) {
+                                             const float* r1, const float* r2, const float* sink, int v_row, int n_splits, float* part_o,
+                                             float* part_ml, void* stream) {
   if (n_tiles <= 0 && n_items <= 0) return 0;
-  if (nkv <= 0 || nq % nkv || ps <= 0 || n_splits < 1 || (n_items > 0 && nq / nkv > 16)) return (int)cudaErrorInvalidValue;
+  if (nkv <= 0 || nq % nkv || ps <= 0 || n_splits < 1 || (n_items > 0 && nq / nkv > 16) || v_row % 8) return (int)cudaErrorInvalidValue;
   BiasedArgs a;
   a.qkv = (const bf16*)qkv; a.qkv_stride = qkv_stride; a.out = (bf16*)out; a.kpages = (const bf16*)kp; a.vpages = (const bf16*)vp;
   a.block_table = bt; a.table_width = tw; a.cu_q = cu; a.q_start_pos = sp; a.items = nullptr;
   a.nq = nq; a.nkv = nkv; a.page_size = ps; a.window = window; a.keep_first = keep;
-  a.scale_log2 = scale * 1.4426950408889634f; a.r1 = r1; a.r2 = r2; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
+  a.scale_log2 = scale * 1.4426950408889634f; a.r1 = r1; a.r2 = r2; a.sink = sink; a.v_row = v_row > 0 ? v_row : dv; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
   cudaStream_t s = (cudaStream_t)stream;
 #define BIASED_CASE(K, V) if (dk == K && dv == V) return biased_mma_launch<K, V>(a, n_tiles, n_items, tiles, items, s);
   BIASED_CASE(32, 32) BIASED_CASE(32, 64) BIASED_CASE(32, 128)

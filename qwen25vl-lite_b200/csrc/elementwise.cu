@@ -272,6 +272,38 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
   }
 }
 
+// Dynamic Tanh, a norm without statistics: x[row] += delta[row] (when given), then
+// out[r] = tanh(alpha * x[row]) * w + b.  rows as in add_rmsnorm_kernel: with rows only those rows
+// are produced and x is left alone.  Nothing is reduced, so a row is just a run of elements.
+template <typename T>
+__global__ void add_dyt_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+                               const float* __restrict__ b, float alpha, T* __restrict__ out, const int* __restrict__ rows,
+                               int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* xr = x + (size_t)row * hidden;
+  const T* dr = delta ? delta + (size_t)row * hidden : nullptr;
+  T* o = out + (size_t)r * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = xr[c];
+    if (dr) {
+      v += to_f32(dr[c]);
+      if (!rows) xr[c] = v;
+    }
+    o[c] = from_f32<T>(fmaf(tanhf(alpha * v), w[c], b[c]));
+  }
+}
+
+// logits <- cap * tanh(logits / cap), in place.
+__global__ void softcap_kernel(float* __restrict__ logits, size_t total, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    logits[i] = cap * tanhf(logits[i] / cap);
+}
+
 template <typename T, bool EXACT>
 static int embed_position_norm(const void* table, const void* pos_table, const int* ids, const int* positions, const float* w,
                                float eps, float* x, int n, int hidden, int vocab, int max_positions, int groups, void* stream) {
@@ -378,3 +410,22 @@ Q25_EXPORT int q25_glu_clamped_bf16(const void* gu, void* o, int n, int inter, f
 
 // Streaming multiprocessors of the current device (0 if it cannot be read).
 Q25_EXPORT int q25_sm_count(void) { return device_sm_count(); }
+
+template <typename T>
+static int add_dyt(float* x, const void* delta, const float* w, const float* b, float alpha, void* out, const int* rows, int n_out,
+                   int hidden, void* stream) {
+  if (n_out <= 0) return 0;
+  launch(add_dyt_kernel<T>, dim3(n_out), dim3(hidden >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, x, (const T*)delta, w, b, alpha,
+         (T*)out, rows, hidden);
+  return launch_status();
+}
+Q25_EXPORT int q25_add_dyt_f32(float* x, const void* d, const float* w, const float* b, float alpha, void* o, const int* rows, int n, int h, void* s) { return add_dyt<float>(x, d, w, b, alpha, o, rows, n, h, s); }
+Q25_EXPORT int q25_add_dyt_bf16(float* x, const void* d, const float* w, const float* b, float alpha, void* o, const int* rows, int n, int h, void* s) { return add_dyt<bf16>(x, d, w, b, alpha, o, rows, n, h, s); }
+Q25_EXPORT int q25_softcap(float* logits, long long total, float cap, void* s) {
+  if (total <= 0) return 0;
+  size_t blocks = ((size_t)total + 255) / 256;
+  const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
+  if (blocks > most) blocks = most;
+  launch(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)s, logits, (size_t)total, cap);
+  return launch_status();
+}

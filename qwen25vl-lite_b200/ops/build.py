@@ -31,7 +31,9 @@ NVCC_FLAGS = [
 # bfloat16 ones; "chain" the weight-streaming product of bfloat16 decode steps; "tcgen05" the
 # tcgen05 product (dense, and grouped by expert); "bf16" the tensor-core attention that only the
 # serving path of rotary softmax attention loads; "recurrent", "biased" and "routed" the kernels of the gated linear recurrence,
-# of attention with a distance bias and kept first tokens, and of the routed feed-forward.  A
+# of attention with a distance bias, kept first tokens or a sink, and of the routed feed-forward; "rotary" a
+# rotation of part of a head in either pairing, "latent" the compressed cache row of latent attention,
+# "retention" the decayed linear attention.  A
 # library is compiled when a model first asks for one of its kernels, so a run compiles only what
 # its model and dtype need.
 LIBRARIES: Dict[str, List[str]] = {
@@ -42,6 +44,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "recurrent": ["recurrent.cu"],
     "biased": ["attention_biased.cu"],
     "routed": ["moe.cu"],
+    "rotary": ["rotary.cu"],
+    "latent": ["latent.cu"],
+    "retention": ["retention.cu"],
 }
 
 

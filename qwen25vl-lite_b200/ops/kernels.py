@@ -31,7 +31,11 @@ _SIGNATURES = {
     "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _P],
     "q25_rglru_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "q25_rglru_scan": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P],
-    "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
+    "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _P],
+    "q25_add_dyt": [_P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
+    "q25_rotary_apply": [_P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "q25_latent_store": [_P, _I, _I, _I, _P, _F, _P, _I, _I, _P, _P, _I, _P],
+    "q25_retention_scan": [_P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _P],
     "q25_kv_store_mix": [_P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
@@ -73,7 +77,8 @@ def load_library(name: str = "core") -> ctypes.CDLL:
 # library is compiled and loaded when one of its kernels is first asked for
 _SYMBOL_LIBRARY = (("q25_gemm_chain", "chain"), ("q25_attention_decode", "bf16"), ("q25_attention_prefill", "bf16"),
                    ("q25_gemm_tcgen05", "tcgen05"), ("q25_rope_angles", "bf16"), ("q25_rglru", "recurrent"),
-                   ("q25_biased_attention", "biased"), ("q25_kv_store_mix", "biased"), ("q25_moe", "routed"))
+                   ("q25_biased_attention", "biased"), ("q25_kv_store_mix", "biased"), ("q25_moe", "routed"),
+                   ("q25_rotary", "rotary"), ("q25_latent", "latent"), ("q25_retention", "retention"))
 
 
 def _library_of(symbol: str) -> str:
@@ -737,13 +742,20 @@ def kv_store_mix(qkv: torch.Tensor, v_other: Optional[torch.Tensor], mix: float,
 def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                              block_table: torch.Tensor, token_seq: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor,
                              nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
-                             r1: Optional[torch.Tensor], r2: Optional[torch.Tensor]) -> None:
+                             r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: Optional[torch.Tensor] = None,
+                             v_row: int = 0) -> None:
+    """``sink`` (float32 [nq]): a score per query head that has no key and no value and joins the
+    softmax's denominator.  ``v_row``: channels between two value rows of a page when the values lie
+    inside the key rows (0: the values have pages of their own, rows of ``dv`` channels)."""
+    if sink is not None:
+        _dev(sink, torch.float32, "attention sink")
     if dv > 256:
         raise KernelError(f"attention: value size {dv} is beyond 256")
     _check(_typed("q25_biased_attention_generic", qkv.dtype)(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), cu_q.data_ptr(), q_start_pos.data_ptr(), qkv.shape[0], nq, nkv, dk, dv,
-        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _stream()), "biased_attention_generic")
+        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _ptr(sink), int(v_row or 0), _stream()),
+        "biased_attention_generic")
 
 
 def biased_attention_mma_supports(dtype: torch.dtype, dk: int, dv: int) -> bool:
@@ -755,7 +767,7 @@ def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                          cu_q: torch.Tensor, q_start_pos: torch.Tensor, tiles: Optional[torch.Tensor], items: Optional[torch.Tensor],
                          nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
                          r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_splits: int = 1,
-                         scratch: Optional[torch.Tensor] = None) -> None:
+                         scratch: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, v_row: int = 0) -> None:
     """Tensor-core attention (bfloat16): ``tiles`` int32 [n, 2] are (entry, tile of 64 (token, head of
     the group) rows) of the runs, ``items`` the entries that bring one token, whose keys are cut into
     ``n_splits`` ranges (partial results through ``scratch``, float32, len(items) * nq * n_splits * (dv + 2))."""
@@ -771,12 +783,103 @@ def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
     if not biased_attention_mma_supports(qkv.dtype, dk, dv) or (n_items and nq // nkv > 16):
         raise KernelError(f"biased_attention_mma: unsupported sizes {dk}/{dv} or more than 16 heads per kv head for single tokens")
     _check(_fn("q25_biased_attention_mma_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P, _P, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), _ptr(tiles), n_tiles, _ptr(items), n_items, nq, nkv, dk, dv,
-        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), int(n_splits), part_o, part_ml,
-        _stream()), "biased_attention_mma")
+        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _ptr(sink), int(v_row or 0), int(n_splits),
+        part_o, part_ml, _stream()), "biased_attention_mma")
     count_replayed((1 if n_tiles and n_items else 0) + (1 if n_items and n_splits > 1 else 0))
+
+
+# ---- a norm without statistics, a cap on the logits -------------------------------------------------
+
+
+def add_dyt(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor, alpha: float,
+            out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """x += delta (when given); out = tanh(alpha * x) * weight + bias.  ``rows`` as for ``add_rmsnorm``."""
+    hidden = x.shape[-1]
+    _dev(x, torch.float32, "add_dyt x"); _dev(weight, torch.float32, "add_dyt weight"); _dev(bias, torch.float32, "add_dyt bias")
+    if delta is not None:
+        _dev(delta, out.dtype, "add_dyt delta")
+    if rows is not None:
+        _dev(rows, torch.int32, "add_dyt rows")
+    _check(_typed("q25_add_dyt", out.dtype)(x.data_ptr(), _ptr(delta), weight.data_ptr(), bias.data_ptr(), float(alpha),
+                                            out.data_ptr(), _ptr(rows), out.shape[0], hidden, _stream()), "add_dyt")
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place (float32)."""
+    _dev(logits, torch.float32, "softcap logits")
+    _check(_fn("q25_softcap", [_P, _LL, _F, _P])(logits.data_ptr(), logits.numel(), float(cap), _stream()), "softcap")
+
+
+# ---- rotary positions on one axis, for part of a head, in either pairing -------------------------------
+
+ROTARY_LAYOUTS = {"interleaved": 0, "halves": 1}
+
+
+def rotary_angles(positions: torch.Tensor, inv_freq: torch.Tensor, magnitude: float) -> torch.Tensor:
+    """float32 [N, len(inv_freq), 2]: (cos, sin) of position * frequency, times ``magnitude``."""
+    n, half = positions.shape[0], inv_freq.shape[0]
+    _dev(positions, torch.int32, "rotary_angles positions"); _dev(inv_freq, torch.float32, "rotary_angles frequencies")
+    out = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    _check(_fn("q25_rotary_angles", [_P, _P, _F, _P, _I, _I, _P])(positions.data_ptr(), inv_freq.data_ptr(), float(magnitude),
+                                                                 out.data_ptr(), n, half, _stream()), "rotary_angles")
+    return out
+
+
+def rotary_apply(src: torch.Tensor, dst: torch.Tensor, heads: int, width: int, angles: torch.Tensor, layout: str) -> None:
+    """For every token and head, ``width`` channels of ``src`` go to ``dst``, the first
+    ``2 * angles.shape[1]`` of them rotated.  src and dst are [N, heads, >= width] views (strided; may be the same
+    memory) whose channels are contiguous."""
+    n = src.shape[0]
+    half = angles.shape[1]
+    if (src.dtype != dst.dtype or src.dim() != 3 or dst.dim() != 3 or src.shape[1] != heads or dst.shape[1] != heads
+            or src.stride(2) != 1 or dst.stride(2) != 1 or dst.shape[0] != n or angles.shape[0] != n or 2 * half > width):
+        raise KernelError("rotary_apply: src and dst are [N, heads, width] views of one dtype with contiguous channels")
+    _check(_typed("q25_rotary_apply", src.dtype)(
+        src.data_ptr(), src.stride(0), src.stride(1), dst.data_ptr(), dst.stride(0), dst.stride(1), n, heads, width, half,
+        ROTARY_LAYOUTS[layout], angles.data_ptr(), _stream()), "rotary_apply")
+
+
+# ---- the latent cache row; retention ----------------------------------------------------------------
+
+
+def latent_store(x: torch.Tensor, rank: int, rot: int, norm_weight: torch.Tensor, eps: float, angles: Optional[torch.Tensor],
+                 layout: str, pages: torch.Tensor, kv_slot: torch.Tensor) -> None:
+    """Rows of ``x`` [N, rank + rot] (a strided view) -> cache rows [rank + rot] at ``kv_slot``: the first
+    ``rank`` channels RMS-normed with the weight, the last ``rot`` rotated by ``angles``."""
+    _dev(norm_weight, torch.float32, "latent_store weight")
+    if x.stride(1) != 1 or x.shape[1] != rank + rot or pages.dtype != x.dtype or pages.shape[-1] != rank + rot:
+        raise KernelError(f"latent_store: rows and pages must hold {rank} + {rot} channels of one dtype")
+    half = 0 if angles is None else angles.shape[1]
+    _check(_typed("q25_latent_store", x.dtype)(x.data_ptr(), x.stride(0), rank, rot, norm_weight.data_ptr(), float(eps), _ptr(angles),
+                                               half, ROTARY_LAYOUTS[layout], pages.data_ptr(), kv_slot.data_ptr(), x.shape[0],
+                                               _stream()), "latent_store")
+
+
+def retention_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: int, angles: Optional[torch.Tensor], layout: str,
+                   decay: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor,
+                   n_seqs: int, heads: int, dim: int, vdim: int, k_scale: float, eps: float) -> None:
+    """Every entry's tokens in order through ``S = decay S + k v^T``, ``o = S^T q`` from the request's
+    ``state`` [slots, heads, dim, vdim] (float32), which moves on; out = unit_rms(o) * silu(g) per head.
+    ``x`` rows hold the q, k, v and g channels at the given offsets; q and k are rotated by ``angles``."""
+    _dev(state, torch.float32, "retention state"); _dev(decay, torch.float32, "retention decay")
+    if tuple(state.shape[1:]) != (heads, dim, vdim) or x.stride(1) != 1 or out.dtype != x.dtype or not out.is_contiguous():
+        raise KernelError(f"retention_scan: state must be [slots, {heads}, {dim}, {vdim}]")
+    half = 0 if angles is None else angles.shape[1]
+    _check(_typed("q25_retention_scan", x.dtype)(
+        x.data_ptr(), x.stride(0), q_off, k_off, v_off, g_off, _ptr(angles), half, ROTARY_LAYOUTS[layout], decay.data_ptr(),
+        state.data_ptr(), cu_q.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), int(n_seqs), heads, dim, vdim, float(k_scale),
+        float(eps), _stream()), "retention_scan")
+
+
+def retention(x: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: int, angles: Optional[torch.Tensor], layout: str,
+              decay: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor,
+              n_seqs: int, max_q_len: int, heads: int, dim: int, vdim: int, k_scale: float, eps: float) -> None:
+    """Retention over a step's entries (see ``retention_scan``)."""
+    retention_scan(x, q_off, k_off, v_off, g_off, angles, layout, decay, state, cu_q, slot_ids, out, n_seqs, heads, dim, vdim,
+                   k_scale, eps)
 
 
 # ---- the routed feed-forward ------------------------------------------------------------------------

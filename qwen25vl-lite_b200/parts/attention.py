@@ -167,3 +167,174 @@ class BiasedWindowAttention(Mixer):
         out = attention_ops.attend_biased(ctx, ctx.plan(self), qkv, kv, nq, nkv, dk, dv, self.window, self.keep_first,
                                           self.scale, self.r1, self.r2)
         return self.o_proj(out)
+
+
+def _sink_tensor(sink, tensors, heads: int, device):
+    """float32 [heads] for the kernels: the learned numbers, zeros for a sink whose score is 0, None for none."""
+    if sink == "learned":
+        return tensors["sink"].to(device=device, dtype=torch.float32).contiguous()
+    if sink == "zero":
+        return torch.zeros(heads, dtype=torch.float32, device=device)
+    return None
+
+
+@register_mixer("sink_attention")
+class SinkAttention(Mixer):
+    """Grouped-query softmax attention with rotated queries and keys, a ``scale`` of its own, values of
+    ``value_dim`` channels, an optional sliding ``window`` (``0 <= i - j < window``; none: causal), no
+    biases, and a *sink* in the softmax: ``p_j = exp(s_j) / (exp(sink_h) + sum_j exp(s_j))``.  The sink
+    has no key and no value; it is ``"learned"`` (one number per query head, the tensor ``sink``),
+    ``"zero"`` (its score is 0: one is added to the denominator) or None.  The layer's position
+    encoding (``position``, a ``rotary``) turns the first channels of every query and key head; values
+    are not turned.  Tensors: ``q``, ``k``, ``v``, ``o`` (and ``sink``)."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+    accepts_residual = True          # the output projection can add into the residual stream itself
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: Optional[int] = None,
+                 scale: Optional[float] = None, window: Optional[int] = None, sink: Optional[str] = None, position=None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads")
+        if sink not in (None, "zero", "learned"):
+            raise ValueError(f"sink is None, 'zero' or 'learned', got {sink!r}")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.value_dim = self.head_dim if value_dim is None else int(value_dim)
+        if not 0 < self.value_dim <= 256 or self.head_dim <= 0:
+            raise ValueError(f"key size {head_dim} / value size {value_dim} is not supported: values take up to 256 channels")
+        self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)
+        self.window = None if not window else int(window)
+        self.sink_kind, self.position = sink, position
+        self.qkv_proj = self.o_proj = self.sink = None
+
+    def tensor_specs(self):
+        h, q = self.hidden_size, self.num_heads * self.head_dim
+        specs = [TensorSpec("q", (q, h)), TensorSpec("k", (self.num_kv_heads * self.head_dim, h)),
+                 TensorSpec("v", (self.num_kv_heads * self.value_dim, h)), TensorSpec("o", (h, self.num_heads * self.value_dim))]
+        if self.sink_kind == "learned":
+            specs.append(TensorSpec("sink", (self.num_heads,), "bias"))
+        return tuple(specs)
+
+    def cache_need(self):
+        return KVCacheNeed(self.num_kv_heads, self.head_dim, self.window, self.value_dim)
+
+    def load(self, tensors, device, dtype):
+        w = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0)
+        self.qkv_proj = Linear(w.to(device=device, dtype=dtype).contiguous())
+        self.o_proj = Linear(tensors["o"].to(device=device, dtype=dtype).contiguous())
+        self.sink = _sink_tensor(self.sink_kind, tensors, self.num_heads, device)
+
+    def plan_key(self):
+        return ("biased_window_attention", self.num_heads // self.num_kv_heads, self.window or 0, 0)
+
+    def plan_step(self, host):
+        return attention_ops.plan_biased(host, self.num_heads // self.num_kv_heads, self.window or 0, 0)
+
+    def forward(self, ctx, h, stop, residual=None):
+        nq, nkv, dk, dv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        qkv = self.qkv_proj(h)
+        if self.position is not None:
+            qk = qkv[:, :(nq + nkv) * dk].unflatten(1, (nq + nkv, dk))       # query heads, then key heads
+            self.position.rotate(ctx, qk, qk, dk)
+        kv = ctx.kv(stop)
+        if stop.owns_cache:
+            kernels.kv_store_mix(qkv, None, 0.0, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, dk, dv, kv.page_size)
+        out = attention_ops.attend_biased(ctx, ctx.plan(self), qkv, kv, nq, nkv, dk, dv, self.window, 0, self.scale, None, None,
+                                          self.sink)
+        return self.o_proj(out, residual=residual)
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    """Multi-head attention whose keys and values are expanded from one small latent per token
+    (DeepSeek-AI, "DeepSeek-V2: A Strong, Economical, and Efficient Mixture-of-Experts Language Model").
+
+    ``q = Wq h``, per head ``head_dim`` plain and ``rot_dim`` rotated channels.  ``Wdkv h`` gives
+    ``kv_rank`` channels that are RMS-normed with a weight into the latent ``c``, and ``rot_dim`` more
+    that are rotated (not normed) into one key part shared by all heads.  Per head the plain key is
+    ``Wuk_h c`` and the value ``Wuv_h c``; ``score = (q_plain . k_plain + q_rot . k_rot) * scale``; a
+    sliding ``window`` and a sink as in ``sink_attention``; ``Wo`` on the concatenated heads.
+
+    Only ``[c | k_rot]`` is cached, one row of ``kv_rank + rot_dim`` channels per token.  Keys and values
+    are never expanded: since ``q_plain . (Wuk_h c) = (Wuk_h^T q_plain) . c``, every head's query is
+    carried into the latent space, attention runs as H query heads over the single cached row as key
+    (value: its first ``kv_rank`` channels), and ``Wuv_h`` is applied to the attended latent.  The two
+    per-head products are batched products of the matrix library in bfloat16 and this engine's
+    ordered FMA product, head by head, in float32."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels and library products
+    accepts_residual = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int, kv_rank: int, scale: float,
+                 norm_eps: float, window: Optional[int] = None, sink: Optional[str] = "learned", position=None):
+        if sink not in (None, "zero", "learned"):
+            raise ValueError(f"sink is None, 'zero' or 'learned', got {sink!r}")
+        self.hidden_size, self.num_heads, self.head_dim, self.rot_dim = int(hidden_size), int(num_heads), int(head_dim), int(rot_dim)
+        self.value_dim, self.kv_rank = int(value_dim), int(kv_rank)
+        if not 0 < self.kv_rank <= 256:
+            raise ValueError(f"the latent takes up to 256 channels, got {kv_rank}")
+        self.scale, self.norm_eps = float(scale), float(norm_eps)
+        self.window = None if not window else int(window)
+        self.sink_kind, self.position = sink, position
+        if position is not None and position.dims > self.rot_dim:
+            raise ValueError(f"the position encoding turns {position.dims} channels, the rotated part has {rot_dim}")
+
+    def tensor_specs(self):
+        h, H, D, R, Dv, C = self.hidden_size, self.num_heads, self.head_dim, self.rot_dim, self.value_dim, self.kv_rank
+        specs = [TensorSpec("q", (H * (D + R), h)), TensorSpec("dkv", (C + R, h)), TensorSpec("dkv.norm", (C,), "norm"),
+                 TensorSpec("uk", (H * D, C)), TensorSpec("uv", (H * Dv, C)), TensorSpec("o", (h, H * Dv))]
+        if self.sink_kind == "learned":
+            specs.append(TensorSpec("sink", (H,), "bias"))
+        return tuple(specs)
+
+    def cache_need(self):
+        return KVCacheNeed(1, self.kv_rank + self.rot_dim, self.window, self.kv_rank, 0, value_in_key=True)
+
+    def load(self, tensors, device, dtype):
+        H, D, Dv, C = self.num_heads, self.head_dim, self.value_dim, self.kv_rank
+        w = torch.cat([tensors["q"], tensors["dkv"]], dim=0)
+        self.in_proj = Linear(w.to(device=device, dtype=dtype).contiguous())
+        self.norm_weight = tensors["dkv.norm"].to(device=device, dtype=torch.float32).contiguous()
+        # per head: [C, D], the matrix that carries a plain query into the latent space (y = x W^T with W = Wuk_h^T)
+        self.uk_t = tensors["uk"].reshape(H, D, C).transpose(1, 2).to(device=device, dtype=dtype).contiguous()
+        self.uv = tensors["uv"].reshape(H, Dv, C).to(device=device, dtype=dtype).contiguous()
+        self.o_proj = Linear(tensors["o"].to(device=device, dtype=dtype).contiguous())
+        self.sink = _sink_tensor(self.sink_kind, tensors, H, device)
+
+    def plan_key(self):
+        return ("biased_window_attention", self.num_heads, self.window or 0, 0)
+
+    def plan_step(self, host):
+        return attention_ops.plan_biased(host, self.num_heads, self.window or 0, 0)
+
+    def _per_head(self, x, w, out):
+        """out[:, h] = x[:, h] @ w[h]^T for [N, H, *] views (strided) and w [H, out, in]."""
+        if x.dtype == torch.float32:
+            for h in range(self.num_heads):
+                kernels.gemm_f32(x[:, h], w[h], None, out[:, h])
+        else:
+            kernels.chain_flush()           # a library product: products that wait in a chain come first
+            torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+
+    def forward(self, ctx, h, stop, residual=None):
+        H, D, R, Dv, C = self.num_heads, self.head_dim, self.rot_dim, self.value_dim, self.kv_rank
+        n = h.shape[0]
+        qd = self.in_proj(h)                                        # [N, H (D + R) | C + R]
+        q = qd[:, :H * (D + R)].unflatten(1, (H, D + R))
+        down = qd[:, H * (D + R):]
+        kv = ctx.kv(stop)
+        angles = self.position.angles(ctx) if self.position is not None else None
+        layout = self.position.layout if self.position is not None else "interleaved"
+        if stop.owns_cache:
+            kernels.latent_store(down, C, R, self.norm_weight, self.norm_eps, angles, layout, kv.k_pages, kv.kv_slot)
+        # every head's query in the latent space, then its rotated part: rows of C + R channels like the cached ones
+        q_lat = torch.empty((n, H, C + R), dtype=qd.dtype, device=qd.device)
+        self._per_head(q[:, :, :D], self.uk_t, q_lat[:, :, :C])
+        if self.position is not None:
+            self.position.rotate(ctx, q[:, :, D:], q_lat[:, :, C:], R)
+        else:
+            q_lat[:, :, C:] = q[:, :, D:]
+        att = attention_ops.attend_biased(ctx, ctx.plan(self), q_lat.view(n, H * (C + R)), kv, H, 1, C + R, C, self.window, 0,
+                                          self.scale, None, None, self.sink, v_row=C + R)
+        out = torch.empty((n, H, Dv), dtype=qd.dtype, device=qd.device)
+        self._per_head(att.view(n, H, C), self.uv, out)
+        return self.o_proj(out.view(n, H * Dv), residual=residual)

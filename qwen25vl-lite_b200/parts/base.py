@@ -36,13 +36,16 @@ class TensorSpec:
 class KVCacheNeed:
     """Pages of keys and values: all keys (window None) or the last ``window`` of them, beside
     which the first ``keep_first`` tokens of the request stay readable for good.  ``value_dim``:
-    the size of a value when it is not the key's."""
+    the size of a value when it is not the key's.  ``value_in_key``: a value is the first
+    ``value_dim`` channels of its key row (a compressed row that serves as both): the group then
+    keeps one tensor of pages, and the values are rows ``head_dim`` channels apart in it."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
     keep_first: int = 0
+    value_in_key: bool = False
 
     @property
     def v_dim(self) -> int:

@@ -21,6 +21,8 @@ class PreNormResidualBlock(Block):
             mixed = mixer.forward(ctx, h, stop, residual=x)
         else:
             mixed = mixer.forward(ctx, h, stop)
+        if ffn is None:                  # a layer of a mixer alone: its update is added by whoever normalises next
+            return mixed
         h = self.norms[1].forward(ctx, x, mixed, defer=ffn.accepts_deferred_norm)
         if ffn.accepts_residual:
             return ffn.forward(ctx, h, residual=x)

@@ -16,18 +16,19 @@ from .base import Part, TensorSpec, register_embedding, register_head
 class TokenEmbedding(Part):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
-    def __init__(self, vocab_size: int, hidden_size: int):
-        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight"):
+        """``name``: what the table is called in a checkpoint, after the part's prefix."""
+        self.vocab_size, self.hidden_size, self.name = int(vocab_size), int(hidden_size), name
         self.weight = None
 
     def tensor_specs(self):
-        return (TensorSpec("weight", (self.vocab_size, self.hidden_size)),)
+        return (TensorSpec(self.name, (self.vocab_size, self.hidden_size)),)
 
     def load(self, tensors, device, dtype):
-        self.weight = tensors["weight"].to(device=device, dtype=dtype).contiguous()
+        self.weight = tensors[self.name].to(device=device, dtype=dtype).contiguous()
 
     def exports(self):
-        return {"weight": self.weight}
+        return {self.name: self.weight}
 
     def forward(self, ctx):
         x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
@@ -78,11 +79,13 @@ class LinearHead(Part):
     accepts_deferred_norm = True     # its product is a ``Linear``, which normalises inside the kernel when it can
 
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool, tied_to: str = "embed_tokens.weight",
-                 name: str = "weight"):
+                 name: str = "weight", softcap: float = 0.0):
         """``tied``: without a weight of its own in the checkpoint the head reads the tensor that
         another part holds under the canonical name ``tied_to`` (the embedding table).  ``name``:
-        what the head's own weight is called in a checkpoint, after the part's prefix."""
+        what the head's own weight is called in a checkpoint, after the part's prefix.
+        ``softcap`` c > 0: the logits become ``c * tanh(logits / c)``."""
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.softcap = float(softcap or 0.0)
         self.tied_to = tied_to
         self.name = name
         self._tied_weight = None
@@ -110,4 +113,7 @@ class LinearHead(Part):
                              "which it is tied to" if self.tied else " and is not tied"))
 
     def forward(self, ctx, h):
-        return self.proj(h, out_dtype=torch.float32)
+        logits = self.proj(h, out_dtype=torch.float32)
+        if self.softcap > 0.0:
+            kernels.softcap(logits, self.softcap)
+        return logits

@@ -164,3 +164,32 @@ class RoutedGLU(FeedForward):
         out = torch.empty((n, self.hidden_size), dtype=ctx.dtype, device=dev)
         kernels.moe_combine(y, pair_row, sg, shared, out, top)
         return out
+
+
+@register_feed_forward("clamped_glu")
+class ClampedGLU(FeedForward):
+    """A dense gated feed-forward with clamped branches, no biases: ``g = min(Wg h, limit)``,
+    ``u = clamp(Wu h, -limit, limit)``, ``Wd (g * sigmoid(alpha g) * (u + 1))``: the form of one expert of
+    ``routed_glu``, used by every token.  gate and up are one product."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+    accepts_residual = True          # the down projection can add into the residual stream itself
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.gate_up_proj = self.down_proj = None
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return (TensorSpec("gate", (i, h)), TensorSpec("up", (i, h)), TensorSpec("down", (h, i)))
+
+    def load(self, tensors, device, dtype):
+        gu = torch.cat([tensors["gate"], tensors["up"]], dim=0)
+        self.gate_up_proj = Linear(gu.to(device=device, dtype=dtype).contiguous())
+        self.down_proj = Linear(tensors["down"].to(device=device, dtype=dtype).contiguous())
+
+    def forward(self, ctx, h, residual=None):
+        act = torch.empty((h.shape[0], self.intermediate_size), dtype=ctx.dtype, device=h.device)
+        kernels.glu_clamped(self.gate_up_proj(h), act, self.limit, self.alpha)
+        return self.down_proj(act, residual=residual)

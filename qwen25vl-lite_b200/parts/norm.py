@@ -63,3 +63,40 @@ class RMSNorm(Norm):
             kernels.add_norm_groups(x, delta, None if post is None else post.weight, 0.0 if post is None else post.eps,
                                     1 if post is None else post.groups, self.weight, self.eps, self.groups, out, rows)
         return out
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh(Norm):
+    """Dynamic Tanh: ``tanh(alpha * x) * w + b`` with a learned scalar ``alpha``; no mean, no variance.
+    In a checkpoint the scalar and the bias stand beside the weight as ``<name>.alpha`` and ``<name>.b``.
+    Fused with the residual update like the other norms: the kernel adds the pending update first."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
+    def __init__(self, dim: int, name: str = "weight", optional: bool = False):
+        self.dim, self.name, self.optional = int(dim), name, bool(optional)
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def tensor_specs(self):
+        o = self.optional
+        return (TensorSpec(self.name, (self.dim,), init="norm", optional=o), TensorSpec(self.name + ".b", (self.dim,), init="bias", optional=o),
+                TensorSpec(self.name + ".alpha", (), init="fraction", optional=o))
+
+    def load(self, tensors, device, dtype):
+        names = (self.name, self.name + ".b", self.name + ".alpha")
+        if not all(n in tensors for n in names):
+            if self.optional:
+                return
+            raise KeyError(next(n for n in names if n not in tensors))
+        self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
+        self.bias = tensors[self.name + ".b"].to(device=device, dtype=torch.float32).contiguous()
+        self.alpha = float(tensors[self.name + ".alpha"].to(torch.float32))
+
+    def forward(self, ctx, x, delta, rows=None, defer=False):
+        if isinstance(delta, PendingUpdate):
+            raise TypeError("dynamic_tanh adds a pending update as it is; it cannot normalise one on its way in")
+        n_out = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n_out, self.dim), dtype=ctx.dtype, device=x.device)
+        kernels.add_dyt(x, delta, self.weight, self.bias, self.alpha, out, rows)
+        return out

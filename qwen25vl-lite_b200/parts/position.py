@@ -126,3 +126,104 @@ class TokenIndex(PositionEncoding):
     def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
         if kv is not None:
             kernels.rope_store(qkv, None, None, None, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, head_dim, kv.page_size)
+
+
+def rotary_frequencies(dims: int, base: float, scaling=None):
+    """(frequencies [dims / 2] in float64, magnitude) of a rotary encoding: ``f_i = base^(-2i/dims)``,
+    optionally scaled for contexts beyond the length the model was trained at.  ``scaling`` is None or
+    a dict with ``kind``:
+
+    * ``"wavelength"`` (the rule of Llama 3.1): with wavelength ``l = 2 pi / f``, ``f`` is kept where
+      ``l < original / high``, divided by ``factor`` where ``l > original / low``, and in between
+      ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``; magnitude 1;
+    * ``"ramp"`` (YaRN: Peng, Quesnelle, Fan, Shippole, "YaRN: Efficient Context Window Extension of
+      Large Language Models"): with ``pair(t) = dims ln(original / (2 pi t)) / (2 ln base)``, the pair
+      that turns t times within the original length, ``lo = max(floor(pair(fast)), 0)``,
+      ``hi = min(ceil(pair(slow)), dims - 1)`` and ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``,
+      the frequency is ``r_i f / factor + (1 - r_i) f``; cos and sin are multiplied by
+      ``0.1 ln(factor) + 1``."""
+    import math
+
+    half = dims // 2
+    freqs = [float(base) ** (-2.0 * i / dims) for i in range(half)]
+    if not scaling:
+        return np.asarray(freqs, dtype=np.float64), 1.0
+    kind = scaling.get("kind")
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    if kind == "wavelength":
+        low, high = float(scaling["low"]), float(scaling["high"])
+        out = []
+        for f in freqs:
+            wavelength = 2.0 * math.pi / f
+            if wavelength < original / high:
+                out.append(f)
+            elif wavelength > original / low:
+                out.append(f / factor)
+            else:
+                s = (original / wavelength - low) / (high - low)
+                out.append((1.0 - s) * f / factor + s * f)
+        return np.asarray(out, dtype=np.float64), 1.0
+    if kind == "ramp":
+        pair = lambda turns: dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+        lo = max(math.floor(pair(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(pair(float(scaling["slow"]))), dims - 1)
+        out = []
+        for i, f in enumerate(freqs):
+            r = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / factor * r + f * (1.0 - r))
+        return np.asarray(out, dtype=np.float64), 0.1 * math.log(factor) + 1.0
+    raise ValueError(f"unknown rotary scaling kind {kind!r}; known: wavelength, ramp")
+
+
+@register_position_encoding("rotary")
+class Rotary(PositionEncoding):
+    """Rotary positions on one axis for the first ``dims`` channels of a head (the rest pass), with
+    either pairing of channels: ``layout`` ``"interleaved"`` turns channel 2i with 2i + 1,
+    ``"halves"`` channel i with i + dims / 2; the pair (u, v) at position p becomes
+    ``(u cos a - v sin a, v cos a + u sin a)``, ``a = p f_i``.  ``scaling``: see
+    :func:`rotary_frequencies`.  Positions and angles are float32 in both dtypes; a step's angles
+    are computed once and shared by every layer with the same table.
+
+    A mixer applies it itself where its layout wants it: ``angles(ctx)`` gives the step's table
+    [N, dims / 2, 2] of (cos, sin), ``rotate(ctx, src, dst, width)`` turns [N, heads, width] views."""
+
+    graph_safe = True
+    axes = 1
+    default_is_linear = True
+
+    def __init__(self, dims: int, base: float, layout: str = "interleaved", scaling=None):
+        self.dims, self.base, self.layout = int(dims), float(base), layout
+        if self.dims < 0 or self.dims % 2:
+            raise ValueError(f"a rotary encoding turns an even number of channels, got {dims}")
+        if layout not in kernels.ROTARY_LAYOUTS:
+            raise ValueError(f"unknown rotary layout {layout!r}; known: {sorted(kernels.ROTARY_LAYOUTS)}")
+        self.scaling = dict(scaling) if scaling else None
+        freqs, self.magnitude = rotary_frequencies(self.dims, self.base, self.scaling)
+        self._freqs = freqs.astype(np.float32)
+        self.inv_freq = None
+
+    def load(self, tensors, device, dtype):
+        self.inv_freq = torch.from_numpy(self._freqs).to(device)
+
+    def default_positions(self, start: int, count: int, offset: int):
+        return np.arange(start + offset, start + offset + count, dtype=np.int64)[None, :]
+
+    def angles(self, ctx):
+        """(cos, sin) of the step's positions, float32 [N, dims / 2, 2]; None when nothing turns."""
+        if self.dims == 0:
+            return None
+        key = ("rotary_angles", id(self))
+        table = ctx.shared.get(key)
+        if table is None:
+            table = ctx.shared[key] = kernels.rotary_angles(ctx.positions[0], self.inv_freq, self.magnitude)
+        return table
+
+    def rotate(self, ctx, src, dst, width: int):
+        """[N, heads, >= width] views: ``width`` channels of every head of ``src`` go to ``dst`` (which
+        may be ``src``), the first ``dims`` of them turned."""
+        if self.dims > width:
+            raise ValueError(f"the encoding turns {self.dims} channels, the head part has {width}")
+        if self.dims == 0 and dst is src:
+            return
+        kernels.rotary_apply(src, dst, src.shape[1], width, self.angles(ctx) if self.dims else
+                             torch.empty((src.shape[0], 0, 2), dtype=torch.float32, device=src.device), self.layout)
