@@ -197,3 +197,35 @@ def forward(config, w, tokens, return_layers=False):
     if cap:
         logits = float(cap) * np.tanh(logits / float(cap))
     return (logits, np.stack(streams)) if return_layers else logits
+
+
+# ---- model folders, generation ---------------------------------------------------------------------
+
+def load_model_dir(folder, dtype=np.float64):
+    """(raw config.json dictionary, tensors by name) of a model folder."""
+    import json
+    import os
+
+    from .decoder import read_safetensors
+
+    with open(os.path.join(folder, "config.json"), encoding="utf-8") as fh:
+        config = json.load(fh)
+    return config, {k: np.asarray(v, dtype=dtype) for k, v in read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+
+
+def forward_logits(config, w, tokens):
+    return forward(config, w, tokens)
+
+
+def greedy_generate(config, w, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(np.argmax(forward(config, w, ids)[-1])))
+    return ids[len(prompt):]
+
+
+def generation_margins(config, w, prompt, generated):
+    """For every generated token: how far its plain logit lies below the largest one at its place."""
+    logits = forward(config, w, list(prompt) + list(generated))
+    at = len(prompt) - 1
+    return [float(logits[at + i].max() - logits[at + i, t]) for i, t in enumerate(generated)]

@@ -1,0 +1,150 @@
+"""The Labolix design in the engine against the plain implementation (``plain/labolix.py``), on tiny
+models of four different make-ups: whole prompts, decoding token by token behind a prompt, portions
+down to two tokens, mixed batches on pools so small that pages and state slots are used again, long
+decoding, and greedy generation through ``LLM.generate``; in 32-bit (equal to the plain
+implementation's float64 up to float32 rounding) and in bfloat16 (weights rounded once, compared on
+the same rounded weights)."""
+
+import numpy as np
+import pytest
+
+import replay_util as ru
+from plain import labolix as plain
+from tiny_labolix import TINY, make_model_dir
+
+pytestmark = pytest.mark.gpu
+
+# Logits of these models have a standard deviation of 2 to 6 and reach 20.  32-bit: three times the
+# largest difference measured on any position of any test below.  bfloat16 against float64 on the same
+# rounded weights: the root mean square over the vocabulary of a position's difference, again three
+# times the largest measured; every mechanism's faults (a key too many, a forgotten sink, a lost
+# state) move logits by 0.1 to 10.
+F32_TOLERANCE = 6e-4
+BF16_TOLERANCE = {"L1": 0.25, "L2": 0.25, "L3": 0.4, "L4": 0.1}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("labolix")
+    return {(name, dtype): make_model_dir(root, name, dtype) for name in TINY for dtype in ("float32", "bfloat16")}
+
+
+def requests_for(name, lengths, seed=0):
+    vocab = TINY[name][0]["vocab"]
+    rng = np.random.default_rng(seed)
+    return {f"q{i}": rng.integers(0, vocab, size=n).tolist() for i, n in enumerate(lengths)}
+
+
+_oracle_cache = {}
+
+
+def oracle(folder, requests):
+    cfg, w = plain.load_model_dir(folder, np.float64)
+    out = {}
+    for rid, ids in requests.items():
+        key = (folder, tuple(ids))
+        if key not in _oracle_cache:
+            _oracle_cache[key] = plain.forward_logits(cfg, w, ids)
+        out[rid] = _oracle_cache[key]
+    return out
+
+
+def check(name, dtype, folders, requests, steps, max_requests=4, max_tokens=None):
+    folder = folders[name, dtype]
+    want = oracle(folder, requests)
+    got, runner = ru.run_in_process(folder, dtype, steps, max_tokens or ru.max_live_tokens(steps), TINY[name][2], max_requests)
+    for rid in requests:
+        assert got[rid].shape == want[rid].shape
+        d = got[rid] - want[rid]
+        if dtype == "float32":
+            err = np.abs(d).max(axis=1)
+            assert err.max() < F32_TOLERANCE, (f"{name} request {rid}: first wrong token {int(np.argmax(err >= F32_TOLERANCE))} "
+                                               f"of {len(err)}, error {err.max():.2e}")
+        else:
+            err = np.sqrt((d * d).mean(axis=1))
+            tol = BF16_TOLERANCE[name]
+            assert err.max() < tol, f"{name} request {rid}: first wrong token {int(np.argmax(err >= tol))} of {len(err)}, error {err.max():.2e}"
+    runner.cache.check(runner.live.values())
+    assert not runner.live and all(n == 0 for n in runner.cache.pages_in_use())
+    return runner
+
+
+LENGTHS = {"L1": [1, 2, 67, 150], "L2": [3, 40, 129], "L3": [5, 260, 31], "L4": [1, 77, 200]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_whole_prompts(folders, name, dtype):
+    requests = requests_for(name, LENGTHS[name])
+    check(name, dtype, folders, requests, ru.whole(requests))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_prompt_then_token_by_token(folders, name, dtype):
+    """The last 60 tokens one by one: every window passes over decoded tokens, and the retention state is
+    carried from the prompt into the single tokens."""
+    requests = requests_for(name, [l for l in LENGTHS[name] if l > 2], seed=1)
+    check(name, dtype, folders, requests, ru.prefill_then_decode(requests, tail=60))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_portions_of_many_sizes(folders, name, dtype):
+    """Cuts in the middle of pages and windows: portions of 2, 3, 1, 17, 5, 64 tokens, and of 16, 2, 31."""
+    requests = requests_for(name, [max(LENGTHS[name]), 37], seed=2)
+    check(name, dtype, folders, requests, ru.portions(requests, [2, 3, 1, 17, 5, 64]))
+    check(name, dtype, folders, requests, ru.portions(requests, [16, 2, 31]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_mixed_batches_reuse_pages_and_slots(folders, name, dtype):
+    """Seven requests through three state slots and a pool that holds just the live ones: portions
+    beside single tokens, unequal lengths, every slot and page used again by a later request; each
+    request's logits equal those it gets alone (the plain implementation sees one request at a time)."""
+    requests = requests_for(name, [90, 7, 130, 33, 2, 61, 48], seed=3)
+    steps = ru.mixed(requests, seed=5, max_live=3, decode_tail=9)
+    runner = check(name, dtype, folders, requests, steps, max_requests=3)
+    assert runner.steps == len(steps)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["L1", "L2"])
+def test_long_decoding(folders, name, dtype):
+    """260 tokens one by one behind a prompt of three: steps replayed from captured graphs, windows of 9,
+    24 and 50 that leave the prompt far behind and give their pages back, a retention state that has
+    decayed through hundreds of steps."""
+    requests = requests_for(name, [263], seed=4)
+    runner = check(name, dtype, folders, requests, ru.prefill_then_decode(requests, tail=260))
+    assert runner.graph_replays > 200
+
+
+def test_a_freed_slot_starts_from_zero(folders):
+    """One state slot: the second request gets the slot the first one left, with its state in it."""
+    requests = requests_for("L4", [40, 25, 33], seed=8)
+    check("L4", "float32", folders, requests, ru.whole(requests), max_requests=1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["L1", "L3"])
+def test_greedy_generation_through_the_scheduler(folders, name, dtype):
+    """``LLM.generate``: the engine's own entry point, scheduler (portions of 16 tokens, three
+    requests on two seats) and sampler; 32-bit reproduces the plain implementation's tokens, bfloat16
+    chooses tokens whose plain logits lie within rounding of the largest."""
+    from qwen25vl_lite import LLM, SamplingParams
+
+    folder = folders[name, dtype]
+    prompts = list(requests_for(name, [5, 41, 18], seed=7).values())
+    llm = LLM(folder, dtype=dtype, num_blocks=24, block_size=TINY[name][2], max_num_seqs=2, max_num_batched_tokens=16)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    cfg, w = plain.load_model_dir(folder, np.float64)
+    far = 0
+    for p, o in zip(prompts, outs):
+        assert len(o.output_token_ids) == 12
+        if dtype == "float32":
+            assert o.output_token_ids == plain.greedy_generate(cfg, w, p, 12)
+        else:
+            far += sum(m > 2 * BF16_TOLERANCE[name] for m in plain.generation_margins(cfg, w, p, o.output_token_ids))
+    assert far == 0
+    llm.runner.cache.check(llm.runner.live.values())
