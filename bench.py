@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at Qwen2.5-VL sizes, random bfloat16 weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b|rirulix]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b|rirulix|labolix]
 
 One "step" is one decode step of the whole batch.  The default run (``--config 3b``) has the 3B
 layer sizes: the headline ``value`` is decoded tokens a second at batch 8 after 2,048-token
@@ -11,7 +11,7 @@ out every step).  The same line carries the 2,048-token prefill, the decode step
 decode at batch 1 and 64, the clocks seen while timing, and the number of this engine's kernel
 launches in the timed region.  ``--config 7b-trace`` runs a continuous-batching trace of 128
 requests at the 7B sizes, ``--config 32b`` decode at batch 1 / 8 / 32 after 8,192-token prompts and
-a 2,048-token prefill at the 32B sizes, ``--config rirulix`` prefill and decode of the Rirulix design
+a 2,048-token prefill at the 32B sizes, ``--config rirulix`` / ``--config labolix`` prefill and decode of the Rirulix / Labolix design
 at a few layer sizes beside this decoder at equal size; each prints one line of its own.
 The engine is single-GPU: for --gpus N > 1 one line says so and the exit code is 2.
 """
@@ -484,10 +484,45 @@ RIRULIX_SIZES = {
 }
 
 
+def _labolix_sizes(width, layers, heads, kv_heads, dim, latent_dim, rot_dim, rank, window, ret_heads, ff, vocab):
+    """A Labolix model of ``layers`` layers (attention, latent attention, retention, and so on) and the
+    Qwen2.5-VL text decoder of equal size beside it: the same width, layers, heads, feed-forward and vocabulary."""
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    attn = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                           "rot": {"dims": dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    latent = {"type": "latent_attention", "mixer": {"heads": heads, "dim": latent_dim, "rot_dim": rot_dim, "vdim": latent_dim, "kv_rank": rank,
+                                                    "scale": (latent_dim + rot_dim) ** -0.5, "mask": {"size": window},
+                                                    "rot": {"dims": rot_dim, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    ret = {"type": "retention", "mixer": {"heads": ret_heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 3 * h / ret_heads) for h in range(ret_heads)],
+                                          "rot": {"dims": 128, "base": 10000.0}}}
+    ours = {"architecture": "Labolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [dict((attn, latent, ret)[i % 3], mlp=mlp) for i in range(layers)]}
+    closest = _sizes(width, layers, heads, kv_heads, ff, vocab, True)
+    closest["text_config"]["rope_scaling"]["mrope_section"] = [dim // 8, 3 * dim // 16, 3 * dim // 16]
+    return ours, closest
+
+
+LABOLIX_SIZES = {
+    "w1024": _labolix_sizes(1024, 6, 8, 2, 128, 64, 32, 64, 1024, 8, 2816, 32000),
+    "w2048": _labolix_sizes(2048, 6, 16, 2, 128, 128, 64, 128, 1024, 16, 5632, 32000),
+    "w2560_d64": _labolix_sizes(2560, 6, 40, 8, 64, 64, 32, 128, 2048, 20, 6912, 32000),
+}
+
+
 def run_rirulix(args):
     """Prefill and decode throughput of the Rirulix design at a few layer sizes, each beside the
     Qwen2.5-VL text decoder of equal size, random weights: a 2,048-token prompt in one step, and
     decode steps at batch 8 and 64 after 1,024-token prompts; one JSON line."""
+    return _run_design(args, "Rirulix", "rirulix", RIRULIX_SIZES)
+
+
+def run_labolix(args):
+    """The same measurement for the Labolix design: a 2,048-token prompt in one step, decode steps at
+    batch 8 and 64 after 1,024-token prompts, each size beside the Qwen2.5-VL text decoder of equal size."""
+    return _run_design(args, "Labolix", "labolix", LABOLIX_SIZES)
+
+
+def _run_design(args, design, label_ours, all_sizes):
     import numpy as np
 
     from qwen25vl_lite import LLM
@@ -499,11 +534,11 @@ def run_rirulix(args):
     clocks.start()
     sizes = {}
     launches = 0
-    for name, pair in RIRULIX_SIZES.items():
+    for name, pair in all_sizes.items():
         if args.only_size and name != args.only_size:
             continue
         sizes[name] = {}
-        for label, cfg in zip(("rirulix", "closest"), pair):
+        for label, cfg in zip((label_ours, "closest"), pair):
             llm = LLM(random_config=cfg, weights_seed=0, dtype=args.dtype, num_blocks=64 * (-(-max(context, prompt_len) // PAGE)) + 8,
                       block_size=PAGE, max_num_seqs=65, max_num_batched_tokens=4096, max_model_len=max(context, prompt_len),
                       cuda_graph=not args.no_cuda_graph)
@@ -518,15 +553,14 @@ def run_rirulix(args):
                 launches += r["launches"]
             sizes[name][label] = point
             del llm
-        sizes[name]["prefill_ratio"] = sizes[name]["rirulix"]["prefill_tokens_per_s"] / sizes[name]["closest"]["prefill_tokens_per_s"]
-        sizes[name]["decode_b8_ratio"] = sizes[name]["rirulix"]["decode_b8_tokens_per_s"] / sizes[name]["closest"]["decode_b8_tokens_per_s"]
-        sizes[name]["decode_b64_ratio"] = sizes[name]["rirulix"]["decode_b64_tokens_per_s"] / sizes[name]["closest"]["decode_b64_tokens_per_s"]
-    head = sizes.get("w2048", next(iter(sizes.values())))["rirulix"]
-    print(json.dumps({"metric": "decode tokens/s, Rirulix design at width 2048 (6 layers), batch 8, 1024-token prompts",
+        for key, what in (("prefill_ratio", "prefill_tokens_per_s"), ("decode_b8_ratio", "decode_b8_tokens_per_s"), ("decode_b64_ratio", "decode_b64_tokens_per_s")):
+            sizes[name][key] = sizes[name][label_ours][what] / sizes[name]["closest"][what]
+    head = sizes.get("w2048", next(iter(sizes.values())))[label_ours]
+    print(json.dumps({"metric": f"decode tokens/s, {design} design at width 2048 (6 layers), batch 8, 1024-token prompts",
                       "value": head["decode_b8_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                       "ms_per_step": head["decode_b8_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                       "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (seeded uniform-random token ids, random-init weights)",
-                      "config": {"model": "Rirulix, random weights", "global_batch": 8, "seq_len": context, "parallelism": "single GPU",
+                      "config": {"model": f"{design}, random weights", "global_batch": 8, "seq_len": context, "parallelism": "single GPU",
                                  "l2": "weights and cache of a step exceed L2 at every size but w1024's decode"},
                       "gpu_launches": launches, "sizes": sizes, "clocks": clocks.stop()}))
     return 0
@@ -544,10 +578,10 @@ def main(argv=None):
     ap.add_argument("--only-batch", type=int, default=0, help="time decode steps at this batch size only (for profilers)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32 times the true 32-bit path of the 3b configuration (fewer --layers advised)")
-    ap.add_argument("--only-size", default="", help="with --config rirulix: one of its sizes only (for profilers)")
-    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b", "rirulix"],
-                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each; rirulix: the "
-                         "Rirulix design at a few layer sizes beside the Qwen2.5-VL decoder of equal size")
+    ap.add_argument("--only-size", default="", help="with --config rirulix or labolix: one of its sizes only (for profilers)")
+    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b", "rirulix", "labolix"],
+                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each; rirulix, labolix: "
+                         "that design at a few layer sizes beside the Qwen2.5-VL decoder of equal size")
     args = ap.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
@@ -559,7 +593,7 @@ def main(argv=None):
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm measures the 3b configuration only"}))
             return 0
         return run_reference(args)
-    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b, "rirulix": run_rirulix}[args.config](args)
+    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b, "rirulix": run_rirulix, "labolix": run_labolix}[args.config](args)
 
 
 if __name__ == "__main__":

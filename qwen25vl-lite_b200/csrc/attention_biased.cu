@@ -1,6 +1,7 @@
 // Softmax attention over the paged cache with a bias that grows with distance, a sliding window
 // beside which the first tokens of the request stay visible, a scale of its own, and values whose
-// size may differ from the keys'.  No rotation: positions enter through the bias alone.
+// size may differ from the keys'.  Nothing is rotated here: positions enter through the bias, or the caller
+// has turned queries and keys before.
 //
 //   score(i, j) = (q_i . k_j) * scale - r1[h] * ln(1 + r2[h] * (i - j))        (r1 == nullptr: no bias)
 //   query i sees key j when j <= i and (i - j < window or j < keep_first)       (window 0: all j <= i)
@@ -591,10 +592,17 @@ static int biased_mma_launch(const BiasedArgs& a, int n_tiles, int n_items, cons
   return launch_status();
 }
 
-// Sizes the tensor-core kernels are built for: keys and values of 32, 64 or 128 channels.
+// Sizes the tensor-core kernels are built for: keys and values of 32, 64 or 128 channels in any pairing, and
+// the rows of a latent cache (keys of a rank plus rotated channels over values of the rank alone):
+// 48 / 32, 80 / 64, 96 / 64, 160 / 128, 192 / 128.
+#define BIASED_SIZES(X) \
+  X(32, 32) X(32, 64) X(32, 128) X(64, 32) X(64, 64) X(64, 128) X(128, 32) X(128, 64) X(128, 128) \
+  X(48, 32) X(80, 64) X(96, 64) X(160, 128) X(192, 128)
 Q25_EXPORT int q25_biased_attention_mma_supports(int dk, int dv) {
-  const bool k = dk == 32 || dk == 64 || dk == 128, v = dv == 32 || dv == 64 || dv == 128;
-  return k && v ? 1 : 0;
+#define BIASED_CASE(K, V) if (dk == K && dv == V) return 1;
+  BIASED_SIZES(BIASED_CASE)
+#undef BIASED_CASE
+  return 0;
 }
 
 // tiles: (entry, row tile of 64 rows) pairs of the runs; items: the entries of one token (groups of
@@ -613,9 +621,7 @@ Q25_EXPORT int q25_biased_attention_mma_bf16(const void* qkv, int qkv_stride, vo
   a.scale_log2 = scale * 1.4426950408889634f; a.r1 = r1; a.r2 = r2; a.sink = sink; a.v_row = v_row > 0 ? v_row : dv; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
   cudaStream_t s = (cudaStream_t)stream;
 #define BIASED_CASE(K, V) if (dk == K && dv == V) return biased_mma_launch<K, V>(a, n_tiles, n_items, tiles, items, s);
-  BIASED_CASE(32, 32) BIASED_CASE(32, 64) BIASED_CASE(32, 128)
-  BIASED_CASE(64, 32) BIASED_CASE(64, 64) BIASED_CASE(64, 128)
-  BIASED_CASE(128, 32) BIASED_CASE(128, 64) BIASED_CASE(128, 128)
+  BIASED_SIZES(BIASED_CASE)
 #undef BIASED_CASE
   return (int)cudaErrorInvalidValue;
 }

@@ -35,7 +35,7 @@ _SIGNATURES = {
     "q25_add_dyt": [_P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
     "q25_rotary_apply": [_P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "q25_latent_store": [_P, _I, _I, _I, _P, _F, _P, _I, _I, _P, _P, _I, _P],
-    "q25_retention_scan": [_P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _P],
+    "q25_retention": [_P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _P, _I, _P, _I, _P, _I, _I, _P],
     "q25_kv_store_mix": [_P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
@@ -758,9 +758,13 @@ def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torc
         "biased_attention_generic")
 
 
+# rows of a latent cache the tensor-core kernels are also built for: (rank + rotated channels, rank)
+BIASED_LATENT_SIZES = ((48, 32), (80, 64), (96, 64), (160, 128), (192, 128))
+
+
 def biased_attention_mma_supports(dtype: torch.dtype, dk: int, dv: int) -> bool:
     """Sizes the tensor-core kernels of this attention are built for; the rest goes to the general kernel."""
-    return dtype == torch.bfloat16 and dk in (32, 64, 128) and dv in (32, 64, 128)
+    return dtype == torch.bfloat16 and ((dk in (32, 64, 128) and dv in (32, 64, 128)) or (dk, dv) in BIASED_LATENT_SIZES)
 
 
 def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
@@ -858,28 +862,48 @@ def latent_store(x: torch.Tensor, rank: int, rot: int, norm_weight: torch.Tensor
                                                _stream()), "latent_store")
 
 
-def retention_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: int, angles: Optional[torch.Tensor], layout: str,
-                   decay: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor,
-                   n_seqs: int, heads: int, dim: int, vdim: int, k_scale: float, eps: float) -> None:
-    """Every entry's tokens in order through ``S = decay S + k v^T``, ``o = S^T q`` from the request's
-    ``state`` [slots, heads, dim, vdim] (float32), which moves on; out = unit_rms(o) * silu(g) per head.
-    ``x`` rows hold the q, k, v and g channels at the given offsets; q and k are rotated by ``angles``."""
-    _dev(state, torch.float32, "retention state"); _dev(decay, torch.float32, "retention decay")
-    if tuple(state.shape[1:]) != (heads, dim, vdim) or x.stride(1) != 1 or out.dtype != x.dtype or not out.is_contiguous():
-        raise KernelError(f"retention_scan: state must be [slots, {heads}, {dim}, {vdim}]")
-    half = 0 if angles is None else angles.shape[1]
-    _check(_typed("q25_retention_scan", x.dtype)(
-        x.data_ptr(), x.stride(0), q_off, k_off, v_off, g_off, _ptr(angles), half, ROTARY_LAYOUTS[layout], decay.data_ptr(),
-        state.data_ptr(), cu_q.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), int(n_seqs), heads, dim, vdim, float(k_scale),
-        float(eps), _stream()), "retention_scan")
+RETENTION_CHUNK = 64        # tokens of a chunk of a long run; entries up to this many tokens are walked whole
 
 
 def retention(x: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: int, angles: Optional[torch.Tensor], layout: str,
               decay: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor,
-              n_seqs: int, max_q_len: int, heads: int, dim: int, vdim: int, k_scale: float, eps: float) -> None:
-    """Retention over a step's entries (see ``retention_scan``)."""
-    retention_scan(x, q_off, k_off, v_off, g_off, angles, layout, decay, state, cu_q, slot_ids, out, n_seqs, heads, dim, vdim,
-                   k_scale, eps)
+              n_seqs: int, max_q_len: int, heads: int, dim: int, vdim: int, k_scale: float, eps: float,
+              chunks: Optional[torch.Tensor] = None, runs: Optional[torch.Tensor] = None, scan_too: bool = True) -> None:
+    """Every entry's tokens in order through ``S = decay S + k v^T``, ``o = S^T q`` from the request's
+    ``state`` [slots, heads, dim, vdim] (float32), which moves on; out = unit_rms(o) * silu(g) per head.
+    ``x`` rows hold the q, k, v and g channels at the given offsets; q and k are rotated by ``angles``.
+    ``chunks`` int32 [n, 4] (entry, first token row, tokens, last of its run) and ``runs`` [m, 3] (entry,
+    first chunk, chunks): the entries of more than ``RETENTION_CHUNK`` tokens cut into chunks that are
+    computed in parallel (two passes and a fold between them); ``scan_too`` False: no other entries."""
+    _dev(state, torch.float32, "retention state"); _dev(decay, torch.float32, "retention decay")
+    if tuple(state.shape[1:]) != (heads, dim, vdim) or x.stride(1) != 1 or out.dtype != x.dtype or not out.is_contiguous():
+        raise KernelError(f"retention: state must be [slots, {heads}, {dim}, {vdim}]")
+    half = 0 if angles is None else angles.shape[1]
+    n_chunks = 0 if chunks is None else chunks.numel() // 4
+    n_runs = 0 if runs is None else runs.numel() // 3
+    sums = torch.empty(n_chunks * heads * dim * vdim, dtype=torch.float32, device=x.device) if n_chunks else None
+    _check(_typed("q25_retention", x.dtype)(
+        x.data_ptr(), x.stride(0), q_off, k_off, v_off, g_off, _ptr(angles), half, ROTARY_LAYOUTS[layout], decay.data_ptr(),
+        state.data_ptr(), cu_q.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), int(n_seqs), heads, dim, vdim, float(k_scale),
+        float(eps), _ptr(chunks), n_chunks, _ptr(runs), n_runs, _ptr(sums), RETENTION_CHUNK, int(scan_too), _stream()), "retention")
+    if n_chunks:
+        count_replayed(2 + int(scan_too))          # the passes over the chunks, launched by the same call
+
+
+def plan_retention(q_lens, chunk: int = RETENTION_CHUNK):
+    """The chunks of a step's long entries for ``retention``: ``chunks`` (entry, first token row, tokens,
+    last of its run), ``runs`` (entry, first chunk, chunks), and whether any entry is left to be walked whole."""
+    chunks, runs, row, short = [], [], 0, False
+    for entry, n in enumerate(q_lens):
+        if n > chunk:
+            pieces = -(-n // chunk)
+            runs.append((entry, len(chunks), pieces))
+            for c in range(pieces):
+                chunks.append((entry, row + c * chunk, min(chunk, n - c * chunk), int(c == pieces - 1)))
+        else:
+            short = True
+        row += n
+    return chunks, runs, short
 
 
 # ---- the routed feed-forward ------------------------------------------------------------------------

@@ -12,13 +12,15 @@ by ``silu(Wg h)`` and projected by ``Wo``.
 
 What is float32 in both dtypes: the rotation, k's scale, S, o, the unit norm and the gate's product.
 A request's state is S, one float32 tensor [heads, dim, value_dim] per slot, zero at admission and
-carried from step to step, so a run of tokens may be cut anywhere.
+carried from step to step, so a run of tokens may be cut anywhere.  Single tokens and short runs are
+walked token by token; a long run is cut into chunks that are computed in parallel (``csrc/retention.cu``).
 """
 
 from __future__ import annotations
 
 from typing import Sequence
 
+import numpy as np
 import torch
 
 from ..ops import kernels
@@ -57,12 +59,22 @@ class Retention(Mixer):
         self.o_proj = Linear(tensors["o"].to(device=device, dtype=dtype).contiguous())
         self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=device)
 
+    def plan_key(self):
+        return ("retention",)                 # the chunks of a step's long runs do not depend on a layer's sizes
+
+    def plan_step(self, host):
+        chunks, runs, short = kernels.plan_retention(host.q_lens)
+        return {"chunks": np.asarray(chunks, dtype=np.int32).reshape(-1), "runs": np.asarray(runs, dtype=np.int32).reshape(-1),
+                "short": np.asarray([1] if short and chunks else [], dtype=np.int32)}
+
     def forward(self, ctx, h, stop, residual=None):
         H, D, Dv = self.num_heads, self.head_dim, self.value_dim
+        plan = ctx.plan(self)
         x = self.in_proj(h)                                          # [N, q | k | v | g]
         angles = self.position.angles(ctx) if self.position is not None else None
         layout = self.position.layout if self.position is not None else "halves"
         out = torch.empty((h.shape[0], H * Dv), dtype=x.dtype, device=x.device)
         kernels.retention(x, 0, H * D, 2 * H * D, 2 * H * D + H * Dv, angles, layout, self.decay, stop.state, ctx.cu_q, ctx.slot_ids,
-                          out, ctx.n_seqs, ctx.max_q_len, H, D, Dv, float(D) ** -0.5, self.norm_eps)
+                          out, ctx.n_seqs, ctx.max_q_len, H, D, Dv, float(D) ** -0.5, self.norm_eps, plan.get("chunks"), plan.get("runs"),
+                          scan_too=plan.get("chunks") is None or plan.get("short") is not None)
         return self.o_proj(out, residual=residual)

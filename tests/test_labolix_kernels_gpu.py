@@ -167,7 +167,8 @@ def tolerance(dtype):
 
 
 # (query heads, kv heads, key size, value size, values inside the keys): sizes of the tensor-core kernels and others
-SHAPES = [(6, 2, 64, 32, False), (4, 4, 32, 64, False), (4, 1, 64, 32, True), (3, 1, 48, 40, True), (20, 1, 128, 64, True), (6, 3, 80, 16, False)]
+SHAPES = [(6, 2, 64, 32, False), (4, 4, 32, 64, False), (4, 1, 64, 32, True), (3, 1, 48, 40, True), (20, 1, 128, 64, True), (6, 3, 80, 16, False),
+          (4, 1, 80, 64, True), (16, 1, 192, 128, True), (3, 1, 48, 32, True), (5, 1, 160, 128, True), (3, 1, 96, 64, True)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -255,9 +256,10 @@ def test_retention_in_portions_with_state(dtype, heads, dim, vdim, dims):
         slots = i32([slot[k] for k in names])
         angles = kernels.rotary_angles(positions, inv_freq, 1.0) if dims else None
         out = torch.empty(rows.shape[0], heads * vdim, dtype=dtype, device=DEV)
+        chunks, runs, short = kernels.plan_retention([step[k] for k in names])       # the run of 130 tokens goes in three chunks, 69 and 70 in two
         kernels.retention(rows, 0, heads * dim, 2 * heads * dim, 2 * heads * dim + heads * vdim, angles, "halves",
                           torch.tensor(decay, dtype=torch.float32, device=DEV), state, cu, slots, out, len(names), max(step.values()),
-                          heads, dim, vdim, dim ** -0.5, 1e-5)
+                          heads, dim, vdim, dim ** -0.5, 1e-5, i32(chunks) if chunks else None, i32(runs) if runs else None, scan_too=short or not chunks)
         at = 0
         for k in names:
             got[k].append(out[at:at + step[k]])
