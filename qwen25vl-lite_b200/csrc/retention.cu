@@ -8,9 +8,10 @@
 // Everything after the projections is float in both dtypes: the rotation, k's scale, S, o, the unit
 // norm and the gate's product; only the result is rounded to the activation dtype.
 //
-// retention_scan_kernel walks tokens one after the other with S in shared memory: one CTA per (piece of
-// work, head), Dv * P threads: thread (j, part) owns column j of S for a P-th of the rows.  Steps of
-// single tokens, and short runs, take it alone, a CTA per entry.  Long runs are cut into chunks (the host
+// The kernels walk tokens one after the other, one CTA per (piece of work, head), thread (j, part) owning
+// column j of S for a P-th of the rows: retention_rows_kernel with those rows in registers (head sizes
+// that 4, 8, 16 or 32 divides), retention_scan_kernel with S in shared memory (any sizes).  Steps of
+// single tokens, and short runs, take the walk alone, a CTA per entry.  Long runs are cut into chunks (the host
 // plans them): every chunk's own sum of decayed k v^T from zero, all chunks in parallel; a short pass
 // that folds the sums onto the request's S in order and leaves each chunk the S before it; then every
 // chunk's outputs, again all in parallel.  Twice the arithmetic, and as many CTAs as the run has chunks.
@@ -138,14 +139,188 @@ __global__ void retention_fold_kernel(RetentionArgs a, const int* __restrict__ r
   const size_t SZ = (size_t)a.D * a.Dv;
   const float* Sreq = a.state + ((size_t)a.slot_ids[entry] * a.heads + head) * SZ;
   const float decay = a.decay[head];
+  constexpr int B = 8;                                       // sums in flight per thread
   for (size_t x = (size_t)blockIdx.z * blockDim.x + threadIdx.x; x < SZ; x += (size_t)gridDim.z * blockDim.x) {
     float s = Sreq[x];
-    for (int c = c0; c < c0 + n; ++c) {
-      float* slot = a.sums + ((size_t)c * a.heads + head) * SZ + x;
-      const float own = c + 1 < c0 + n ? *slot : 0.f;      // the last chunk left none
-      *slot = s;
-      s = fmaf(powf(decay, (float)a.chunks[4 * c + 2]), s, own);
+    for (int b0 = 0; b0 < n; b0 += B) {
+      float own[B];
+#pragma unroll
+      for (int i = 0; i < B; ++i) {
+        const int c = c0 + b0 + i;
+        own[i] = b0 + i + 1 < n ? __ldcg(a.sums + ((size_t)c * a.heads + head) * SZ + x) : 0.f;   // the last chunk left none
+      }
+#pragma unroll
+      for (int i = 0; i < B; ++i) {
+        if (b0 + i < n) {
+          const int c = c0 + b0 + i;
+          a.sums[((size_t)c * a.heads + head) * SZ + x] = s;
+          s = fmaf(powf(decay, (float)a.chunks[4 * c + 2]), s, own[i]);
+        }
+      }
     }
+  }
+}
+
+// The same walk with the thread's rows of S in registers, for head sizes that ROWS divides: thread
+// (j, part) owns rows part * ROWS .. of column j.  Four more warps only load: they rotate and scale the
+// keys and queries of the next RET_TB tokens into one half of a double buffer (with the values) while
+// the others work through the half before, so that no trip to memory stands in the walk; the CTA meets
+// once per RET_TB tokens.  The raw outputs of up to `group` tokens wait in shared memory, each part's
+// share apart, and are normalised and gated afterwards, a warp per token.  mode as MODE above.
+#define RET_TB 4
+#define RET_LOADERS 128
+#define RET_MAX_THREADS 640   // 512 that compute and the loaders: registers for 32 rows of S a thread
+
+template <typename T, int ROWS>
+__global__ void __launch_bounds__(RET_MAX_THREADS) retention_rows_kernel(RetentionArgs a, int mode, int long_from, int group) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float ret_smem[];
+  const int D = a.D, Dv = a.Dv, P = D / ROWS;
+  float2* kq = reinterpret_cast<float2*>(ret_smem);   // [2][RET_TB][D]: (scaled rotated key, rotated query)
+  float* vs = ret_smem + 2 * 2 * RET_TB * D;          // [2][RET_TB][Dv]
+  float* obuf = vs + 2 * RET_TB * Dv;                 // [P][group][Dv]
+  const int head = blockIdx.y;
+  int entry, first, last;
+  bool is_last = true;
+  if (mode == 0) {
+    entry = blockIdx.x;
+    first = a.cu_q[entry];
+    last = a.cu_q[entry + 1];
+    if (long_from > 0 && last - first > long_from) return;
+  } else {
+    const int* c = a.chunks + 4 * blockIdx.x;
+    entry = c[0];
+    first = c[1];
+    last = first + c[2];
+    is_last = c[3] != 0;
+    if (mode == 1 && is_last) return;
+  }
+  const size_t SZ = (size_t)D * Dv;
+  float* Sreq = a.state + ((size_t)a.slot_ids[entry] * a.heads + head) * SZ;
+  float* Ssum = mode == 0 ? nullptr : a.sums + ((size_t)blockIdx.x * a.heads + head) * SZ;
+  const float* Sin = mode == 0 ? Sreq : Ssum;
+  const int n_compute = blockDim.x - RET_LOADERS;
+  const bool loader = (int)threadIdx.x >= n_compute;
+  const int ltid = (int)threadIdx.x - n_compute;
+  const bool active = !loader && (int)threadIdx.x < Dv * P;
+  const int j = threadIdx.x % Dv, p = threadIdx.x / Dv, i0 = p * ROWS;
+  float s[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) s[r] = active && mode != 1 ? Sin[(size_t)(i0 + r) * Dv + j] : 0.f;
+  const float decay = a.decay[head];
+  const T* X = reinterpret_cast<const T*>(a.x);
+
+  for (int g0 = first; g0 < last; g0 += group) {
+    const int cnt = min(group, last - g0), nb = (cnt + RET_TB - 1) / RET_TB;
+    // The loaders' part.  A loader keeps its channel and walks the batch's tokens, so that nothing is
+    // divided and all loads of a batch are asked for before any is used: one trip to memory a batch.
+    auto fill = [&](int b) {
+      const int t0 = g0 + b * RET_TB, nt = min(RET_TB, g0 + cnt - t0), base = (b & 1) * RET_TB;
+      const int half = a.angles ? a.half : 0, turned = 2 * half;
+      for (int c = ltid; c < (D > Dv ? D : Dv); c += RET_LOADERS) {
+        int iu = c, iv = c, i = 0;
+        bool second = false;
+        if (c < turned) {                                     // the pair (u, v) this channel belongs to, and which of the two it is
+          if (a.layout == ROTARY_INTERLEAVED) { i = c >> 1; iu = 2 * i; iv = iu + 1; second = c & 1; }
+          else { second = c >= half; i = second ? c - half : c; iu = i; iv = i + half; }
+        }
+        const bool is_k = c < D, is_v = c < Dv, turn = c < turned;
+        // Every load of the batch is asked for before the first is used: the addresses are clamped to
+        // valid ones instead of guarded (a branch would put the first use, and its wait, between the
+        // loads), and the values stay as they were loaded until the second loop.
+        const int cv = is_v ? c : 0, ck_u = is_k ? iu : 0, ck_v = is_k ? iv : 0, ia = turn ? i : 0;
+        const T* row0 = X + (size_t)t0 * a.x_row;
+        const float* ang0 = a.angles ? a.angles + ((size_t)t0 * half + ia) * 2 : nullptr;
+        T raw[RET_TB], ku[RET_TB], kv[RET_TB], qu[RET_TB], qv[RET_TB];
+        float2 cssn[RET_TB];
+#pragma unroll
+        for (int tt = 0; tt < RET_TB; ++tt) {
+          const int tc = tt < nt ? tt : nt - 1;
+          const T* row = row0 + (size_t)tc * a.x_row;
+          raw[tt] = row[a.v_off + (size_t)head * Dv + cv];
+          ku[tt] = row[a.k_off + (size_t)head * D + ck_u];
+          kv[tt] = row[a.k_off + (size_t)head * D + ck_v];
+          qu[tt] = row[a.q_off + (size_t)head * D + ck_u];
+          qv[tt] = row[a.q_off + (size_t)head * D + ck_v];
+          cssn[tt] = ang0 ? *reinterpret_cast<const float2*>(ang0 + (size_t)tc * half * 2) : make_float2(1.f, 0.f);
+        }
+#pragma unroll
+        for (int tt = 0; tt < RET_TB; ++tt) {
+          if (tt < nt) {
+            if (is_v) vs[(base + tt) * Dv + c] = to_f32(raw[tt]);
+            if (is_k) {
+              const float u = to_f32(ku[tt]), v = to_f32(kv[tt]), uq = to_f32(qu[tt]), vq = to_f32(qv[tt]);
+              const float cs = cssn[tt].x, sn = cssn[tt].y;
+              float kk, qq;
+              if (!turn) { kk = u; qq = uq; }
+              else if (second) { kk = fmaf(v, cs, u * sn); qq = fmaf(vq, cs, uq * sn); }
+              else { kk = fmaf(u, cs, -v * sn); qq = fmaf(uq, cs, -vq * sn); }
+              kq[(base + tt) * D + c] = make_float2(kk * a.k_scale, mode == 1 ? 0.f : qq);
+            }
+          }
+        }
+      }
+    };
+    if (loader) fill(0);
+    __syncthreads();
+    for (int b = 0; b < nb; ++b) {
+      if (loader) {
+        if (b + 1 < nb) fill(b + 1);
+      } else if (active) {
+        const int t_end = min(cnt, (b + 1) * RET_TB);
+        for (int t = b * RET_TB; t < t_end; ++t) {
+          const int slot = (b & 1) * RET_TB + (t - b * RET_TB);
+          const float vj = vs[slot * Dv + j];
+          const float2* row = kq + slot * D + i0;
+          float acc = 0.f;
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            const float2 x = row[r];
+            s[r] = fmaf(decay, s[r], x.x * vj);
+            acc = fmaf(s[r], x.y, acc);
+          }
+          if (mode != 1) obuf[((size_t)p * group + t) * Dv + j] = acc;
+        }
+      }
+      __syncthreads();
+    }
+    if (mode != 1) {
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+      for (int t = warp; t < cnt; t += nwarps) {
+        const size_t tok = (size_t)(g0 + t);
+        const T* grow = X + tok * a.x_row + a.g_off + (size_t)head * Dv;
+        T gate[4];                                                       // the first 128 channels' gates, asked for ahead of the sums
+#pragma unroll
+        for (int u = 0; u < 4; ++u) gate[u] = grow[min(lane + 32 * u, Dv - 1)];
+        float ss = 0.f;
+        for (int jj = lane; jj < Dv; jj += 32) {
+          float o = 0.f;
+          for (int pp = 0; pp < P; ++pp) o += obuf[((size_t)pp * group + t) * Dv + jj];
+          obuf[(size_t)t * Dv + jj] = o;                                  // part 0's place now holds the sum (this lane's own element)
+          ss = fmaf(o, o, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
+        T* orow = reinterpret_cast<T*>(a.out) + tok * a.heads * Dv + (size_t)head * Dv;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int jj = lane + 32 * u;
+          const float g = to_f32(gate[u]);
+          if (jj < Dv) orow[jj] = from_f32<T>(obuf[(size_t)t * Dv + jj] * inv * (g / (1.0f + expf(-g))));
+        }
+        for (int jj = lane + 128; jj < Dv; jj += 32) {
+          const float g = to_f32(grow[jj]);
+          orow[jj] = from_f32<T>(obuf[(size_t)t * Dv + jj] * inv * (g / (1.0f + expf(-g))));
+        }
+      }
+      __syncthreads();                                 // the outputs' places are free for the next tokens
+    }
+  }
+  float* Sout = mode == 1 ? Ssum : (is_last ? Sreq : nullptr);
+  if (Sout && active) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) Sout[(size_t)(i0 + r) * Dv + j] = s[r];
   }
 }
 
@@ -174,6 +349,37 @@ static int retention_run(const void* x, int x_row, int q_off, int k_off, int v_o
   a.angles = angles; a.half = half; a.layout = layout; a.decay = decay; a.state = state; a.cu_q = cu_q; a.slot_ids = slot_ids;
   a.out = out; a.heads = heads; a.D = D; a.Dv = Dv; a.P = retention_parts(D, Dv); a.k_scale = k_scale; a.eps = eps;
   a.chunks = chunks; a.sums = sums;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int per = (int)(((size_t)D * Dv + 255) / 256);
+  const dim3 fold_grid(n_runs > 0 ? n_runs : 1, heads, per < 64 ? per : 64);
+  // S in registers where the head size has a divisor among the row counts the kernel is built for
+  int rows = 0;
+  for (int r = 32; r >= 4; r >>= 1)
+    if (D % r == 0) { rows = r; break; }
+  if (rows) {
+    const int P = D / rows, compute = (Dv * P + 31) / 32 * 32;
+    int group = 16384 / (P * Dv);
+    group = group > 64 ? 64 : (group < 1 ? 1 : group);
+    const size_t smem = ((size_t)2 * 2 * RET_TB * D + (size_t)2 * RET_TB * Dv + (size_t)P * group * Dv) * sizeof(float);
+    if (compute + RET_LOADERS <= RET_MAX_THREADS && smem <= 200 * 1024) {
+      void (*kernel)(RetentionArgs, int, int, int) =
+          rows == 32 ? retention_rows_kernel<T, 32> : rows == 16 ? retention_rows_kernel<T, 16>
+          : rows == 8 ? retention_rows_kernel<T, 8> : retention_rows_kernel<T, 4>;
+      if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+      }
+      const dim3 block(compute + RET_LOADERS);
+      if (scan_too) launch(kernel, dim3(n_seqs, heads), block, smem, s, a, 0, n_chunks > 0 ? long_from : 0, group);
+      if (n_chunks > 0) {
+        launch(kernel, dim3(n_chunks, heads), block, smem, s, a, 1, 0, group);
+        launch(retention_fold_kernel, fold_grid, dim3(256), 0, s, a, runs);
+        launch(kernel, dim3(n_chunks, heads), block, smem, s, a, 2, 0, group);
+      }
+      return launch_status();
+    }
+  }
+  // any other sizes: S in shared memory
   const size_t smem = ((size_t)D * Dv + 2 * D + (size_t)a.P * Dv + 32) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
@@ -183,12 +389,10 @@ static int retention_run(const void* x, int x_row, int q_off, int k_off, int v_o
     if (e != cudaSuccess) return (int)e;
   }
   const dim3 block((Dv * a.P + 31) / 32 * 32);
-  cudaStream_t s = (cudaStream_t)stream;
   if (scan_too) launch(retention_scan_kernel<T, 0>, dim3(n_seqs, heads), block, smem, s, a, n_chunks > 0 ? long_from : 0);
   if (n_chunks > 0) {
     launch(retention_scan_kernel<T, 1>, dim3(n_chunks, heads), block, smem, s, a, 0);
-    const int per = (int)(((size_t)D * Dv + 255) / 256);
-    launch(retention_fold_kernel, dim3(n_runs, heads, per < 8 ? per : 8), dim3(256), 0, s, a, runs);
+    launch(retention_fold_kernel, fold_grid, dim3(256), 0, s, a, runs);
     launch(retention_scan_kernel<T, 2>, dim3(n_chunks, heads), block, smem, s, a, 0);
   }
   return launch_status();
