@@ -245,22 +245,25 @@ __global__ void add_norm_groups_kernel(float* __restrict__ x, const T* __restric
 // Gated linear unit with clamped branches: gu is [n, 2*inter], gate in the first half of a row, up
 // in the second; g = min(g, limit), u = clamp(u, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1).
 template <typename T, bool VEC>
-__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter, float limit, float alpha) {
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter, float limit, float alpha,
+                                   int paired) {
   pdl_trigger();
   pdl_wait();
   constexpr int STEP = VEC ? 4 : 1;                     // VEC: inter is a multiple of 4 and the rows start on 16-byte boundaries
   const size_t total = (size_t)n * inter / STEP;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i * STEP / inter, c = i * STEP % inter;
-    const T* g_at = gu + row * 2 * inter + c;
+    // paired: groups of 8 gate features followed by their 8 up features (a run of 4 stays inside a group)
+    const T* g_at = gu + row * 2 * inter + (paired ? (c >> 3) * 16 + (c & 7) : c);
+    const size_t up_at = paired ? 8 : inter;
     float g[4], u[4];
     if (VEC) {
-      const float4 gv = load4<T>(g_at), uv = load4<T>(g_at + inter);
+      const float4 gv = load4<T>(g_at), uv = load4<T>(g_at + up_at);
       g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
       u[0] = uv.x; u[1] = uv.y; u[2] = uv.z; u[3] = uv.w;
     } else {
       g[0] = to_f32(g_at[0]);
-      u[0] = to_f32(g_at[inter]);
+      u[0] = to_f32(g_at[up_at]);
     }
 #pragma unroll
     for (int k = 0; k < STEP; ++k) {
@@ -275,7 +278,7 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
 // Dynamic Tanh, a norm without statistics: x[row] += delta[row] (when given), then
 // out[r] = tanh(alpha * x[row]) * w + b.  rows as in add_rmsnorm_kernel: with rows only those rows
 // are produced and x is left alone.  Nothing is reduced, so a row is just a run of elements.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void add_dyt_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
                                const float* __restrict__ b, float alpha, T* __restrict__ out, const int* __restrict__ rows,
                                int hidden) {
@@ -286,13 +289,27 @@ __global__ void add_dyt_kernel(float* __restrict__ x, const T* __restrict__ delt
   float* xr = x + (size_t)row * hidden;
   const T* dr = delta ? delta + (size_t)row * hidden : nullptr;
   T* o = out + (size_t)r * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-    float v = xr[c];
-    if (dr) {
-      v += to_f32(dr[c]);
-      if (!rows) xr[c] = v;
+  if (VEC) {                                    // hidden is a multiple of 4 and every row starts on a 16-byte boundary
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + c);
+      if (dr) {
+        const float4 d = load4<T>(dr + c);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        if (!rows) *reinterpret_cast<float4*>(xr + c) = v;
+      }
+      const float4 ww = *reinterpret_cast<const float4*>(w + c), bb = *reinterpret_cast<const float4*>(b + c);
+      store4<T>(o + c, make_float4(fmaf(tanhf(alpha * v.x), ww.x, bb.x), fmaf(tanhf(alpha * v.y), ww.y, bb.y),
+                                   fmaf(tanhf(alpha * v.z), ww.z, bb.z), fmaf(tanhf(alpha * v.w), ww.w, bb.w)));
     }
-    o[c] = from_f32<T>(fmaf(tanhf(alpha * v), w[c], b[c]));
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float v = xr[c];
+      if (dr) {
+        v += to_f32(dr[c]);
+        if (!rows) xr[c] = v;
+      }
+      o[c] = from_f32<T>(fmaf(tanhf(alpha * v), w[c], b[c]));
+    }
   }
 }
 
@@ -346,15 +363,16 @@ static int add_norm_groups(float* x, const void* delta, const float* dw, float d
 }
 
 template <typename T>
-static int glu_clamped(const void* gu, void* out, int n, int inter, float limit, float alpha, void* stream) {
+static int glu_clamped(const void* gu, void* out, int n, int inter, float limit, float alpha, int paired, void* stream) {
   if (n <= 0) return 0;
+  if (paired && inter % 8) return (int)cudaErrorInvalidValue;
   const bool vec = inter % 4 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15);
   const size_t total = (size_t)n * inter / (vec ? 4 : 1);
   size_t blocks = (total + 255) / 256;
   const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
   if (blocks > most) blocks = most;
-  if (vec) launch(glu_clamped_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha);
-  else launch(glu_clamped_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha);
+  if (vec) launch(glu_clamped_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha, paired);
+  else launch(glu_clamped_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha, paired);
   return launch_status();
 }
 
@@ -405,8 +423,8 @@ Q25_EXPORT int q25_embed_position_norm_f32(const void* t, const void* pt, const 
 Q25_EXPORT int q25_embed_position_norm_bf16(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, void* s) { return embed_position_norm<bf16, false>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, s); }
 Q25_EXPORT int q25_add_norm_groups_f32(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<float, true>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
 Q25_EXPORT int q25_add_norm_groups_bf16(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<bf16, false>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
-Q25_EXPORT int q25_glu_clamped_f32(const void* gu, void* o, int n, int inter, float limit, float alpha, void* s) { return glu_clamped<float>(gu, o, n, inter, limit, alpha, s); }
-Q25_EXPORT int q25_glu_clamped_bf16(const void* gu, void* o, int n, int inter, float limit, float alpha, void* s) { return glu_clamped<bf16>(gu, o, n, inter, limit, alpha, s); }
+Q25_EXPORT int q25_glu_clamped_f32(const void* gu, void* o, int n, int inter, float limit, float alpha, int paired, void* s) { return glu_clamped<float>(gu, o, n, inter, limit, alpha, paired, s); }
+Q25_EXPORT int q25_glu_clamped_bf16(const void* gu, void* o, int n, int inter, float limit, float alpha, int paired, void* s) { return glu_clamped<bf16>(gu, o, n, inter, limit, alpha, paired, s); }
 
 // Streaming multiprocessors of the current device (0 if it cannot be read).
 Q25_EXPORT int q25_sm_count(void) { return device_sm_count(); }
@@ -415,8 +433,10 @@ template <typename T>
 static int add_dyt(float* x, const void* delta, const float* w, const float* b, float alpha, void* out, const int* rows, int n_out,
                    int hidden, void* stream) {
   if (n_out <= 0) return 0;
-  launch(add_dyt_kernel<T>, dim3(n_out), dim3(hidden >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, x, (const T*)delta, w, b, alpha,
-         (T*)out, rows, hidden);
+  const bool vec = hidden % 4 == 0 && !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)b | (uintptr_t)out) & 15);
+  const dim3 block(hidden >= 1024 ? 256 : 128);
+  if (vec) launch(add_dyt_kernel<T, true>, dim3(n_out), block, 0, (cudaStream_t)stream, x, (const T*)delta, w, b, alpha, (T*)out, rows, hidden);
+  else launch(add_dyt_kernel<T, false>, dim3(n_out), block, 0, (cudaStream_t)stream, x, (const T*)delta, w, b, alpha, (T*)out, rows, hidden);
   return launch_status();
 }
 Q25_EXPORT int q25_add_dyt_f32(float* x, const void* d, const float* w, const float* b, float alpha, void* o, const int* rows, int n, int h, void* s) { return add_dyt<float>(x, d, w, b, alpha, o, rows, n, h, s); }

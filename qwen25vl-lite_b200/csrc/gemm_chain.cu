@@ -55,7 +55,9 @@
 // *err, stops waiting anywhere and runs to its end (its output is then invalid).
 #include "common.cuh"
 
-enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4 };
+// EPI_GLU: the clamped gated unit g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), in the
+// layout of EPI_SWIGLU; its two constants (limit, alpha) are read where EPI_BIAS reads its bias.
+enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4, EPI_GLU = 5 };
 
 #define GC_ROWS 16
 #define GC_MAX_M 8                               // rows of x: one 8-column tile of the MMA (MT = 1).  A second tile
@@ -165,12 +167,19 @@ __device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int gr
     for (int e = 0; e < 2; ++e) {
       const int m = mt * 8 + 2 * t + e;
       if (m >= op.M) continue;
-      if (op.epi == EPI_SWIGLU) {
+      if (op.epi == EPI_SWIGLU || op.epi == EPI_GLU) {
         // rows g of the group are gate features, rows g + 8 the matching up features
         if (row0 + g + 8 < op.N) {
           const float gate = acc[mt][e], up = acc[mt][e + 2];
-          reinterpret_cast<bf16*>(op.out)[(size_t)m * op.ldo + (row0 >> 1) + g] =
-              __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+          float y;
+          if (op.epi == EPI_GLU) {
+            const float limit = op.bias[0], alpha = op.bias[1];
+            const float gg = fminf(gate, limit), uu = fminf(fmaxf(up, -limit), limit);
+            y = gg / (1.0f + __expf(-alpha * gg)) * (uu + 1.0f);
+          } else {
+            y = gate / (1.0f + __expf(-gate)) * up;
+          }
+          reinterpret_cast<bf16*>(op.out)[(size_t)m * op.ldo + (row0 >> 1) + g] = __float2bfloat16_rn(y);
         }
         continue;
       }
@@ -734,7 +743,9 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int sms, int limit, int
   if (d.M <= 0 || d.M > GC_MAX_M || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
   if (((unsigned long long)d.W & 15) || ((unsigned long long)d.X & 15)) return false;
   if (d.norm ? (d.ldx % 4 || !d.norm_w) : (d.ldx % 8 != 0)) return false;
-  if ((d.epi == EPI_SWIGLU && d.N % 16) || (d.epi == EPI_BIAS && !d.bias) || d.epi < 0 || d.epi > EPI_RESIDUAL) return false;
+  if (((d.epi == EPI_SWIGLU || d.epi == EPI_GLU) && d.N % 16) || ((d.epi == EPI_BIAS || d.epi == EPI_GLU) && !d.bias) || d.epi < 0 ||
+      d.epi > EPI_GLU)
+    return false;
   op.W = (const bf16*)d.W; op.X = d.X; op.norm_w = d.norm_w; op.bias = d.bias; op.out = d.out;
   op.ldx = d.ldx; op.ldo = d.ldo; op.M = d.M; op.N = d.N; op.K = d.K; op.epi = d.epi; op.norm = d.norm; op.eps = d.eps;
   op.groups = (d.N + GC_ROWS - 1) / GC_ROWS;

@@ -26,7 +26,9 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
-enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4 };
+// T5_GLU: the clamped gated unit g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), in the
+// layout of T5_SWIGLU; its two constants (limit, alpha) are read where the other epilogues read a bias.
+enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4, T5_GLU = 5 };
 
 #define T5_BM 128
 #define T5_BK 64
@@ -60,8 +62,9 @@ struct T5Shared {
 template <int EPI>
 __device__ __forceinline__ void t5_emit32(const float (&v)[32], int m, int n, int N, const float* __restrict__ bias,
                                           void* __restrict__ out, int ldo) {
-  if constexpr (EPI == T5_SWIGLU) {
+  if constexpr (EPI == T5_SWIGLU || EPI == T5_GLU) {
     // columns come in groups of 16: 8 gate features, then their 8 up features
+    const float limit = EPI == T5_GLU ? bias[0] : 0.f, alpha = EPI == T5_GLU ? bias[1] : 0.f;
     bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + (n >> 1);
 #pragma unroll
     for (int grp = 0; grp < 2; ++grp) {
@@ -70,7 +73,12 @@ __device__ __forceinline__ void t5_emit32(const float (&v)[32], int m, int n, in
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float gate = v[grp * 16 + j], up = v[grp * 16 + 8 + j];
-        o8[j] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+        if constexpr (EPI == T5_GLU) {
+          const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+          o8[j] = __float2bfloat16_rn(g / (1.0f + __expf(-alpha * g)) * (u + 1.0f));
+        } else {
+          o8[j] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+        }
       }
       *reinterpret_cast<uint4*>(dst + grp * 8) = *reinterpret_cast<const uint4*>(o8);
     }
@@ -578,7 +586,7 @@ static int pick_bn(int M, int N) {
 Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, const float* bias, void* out, int ldo, int M,
                                      int N, int K, int epi, int* err, void* stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err || (epi == T5_SWIGLU && N % 16) ||
+  if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err || ((epi == T5_SWIGLU || epi == T5_GLU) && N % 16) || (epi == T5_GLU && !bias) ||
       (epi == T5_BIAS && !bias))
     return (int)cudaErrorInvalidValue;
   CUtensorMap mx, mw;
@@ -596,6 +604,7 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
       case T5_F32: return launch_pair<T5_F32>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
       case T5_SWIGLU: return launch_pair<T5_SWIGLU>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
       case T5_RESIDUAL: return launch_pair<T5_RESIDUAL>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
+      case T5_GLU: return launch_pair<T5_GLU>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
       default: return (int)cudaErrorInvalidValue;
     }
   }
@@ -610,6 +619,7 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
     T5_CASE(T5_F32)
     T5_CASE(T5_SWIGLU)
     T5_CASE(T5_RESIDUAL)
+    T5_CASE(T5_GLU)
     default: return (int)cudaErrorInvalidValue;
   }
 #undef T5_CASE

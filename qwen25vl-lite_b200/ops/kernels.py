@@ -28,7 +28,7 @@ _SIGNATURES = {
     "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "q25_embed_position_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P],
     "q25_add_norm_groups": [_P, _P, _P, _F, _I, _P, _F, _I, _P, _P, _I, _I, _P],
-    "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _P],
+    "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _I, _P],
     "q25_rglru_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "q25_rglru_scan": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P],
     "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _P],
@@ -394,7 +394,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         _stream()), "gemm_f32")
 
 
-SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU, SKINNY_RESIDUAL = 0, 1, 2, 3, 4
+SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU, SKINNY_RESIDUAL, SKINNY_GLU = 0, 1, 2, 3, 4, 5
 # Rows the weight-streaming kernel takes: the 8 batch columns of one m16n8k16 MMA.  A variant with two
 # column tiles ran 9 to 16 rows; measured against the library path on B200 it lost at every size (a
 # decode step of 9 / 12 / 16 requests at the 3B sizes 2.64 / 2.66 / 2.65 ms against 2.43 / 2.55 / 2.59,
@@ -420,8 +420,9 @@ def gemm_skinny_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
     """out = x . w^T for at most 8 rows of x, streaming the weights once (bfloat16).
     ``epilogue``: SKINNY_STORE, SKINNY_BIAS (float32 bias), SKINNY_F32 (float32 out),
-    SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns)
-    or SKINNY_RESIDUAL (out is float32 and the product is added into it).  Runs as an operation
+    SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns),
+    SKINNY_GLU (the same layout with the clamped gated unit; ``bias`` then holds its two constants,
+    float32 [limit, alpha]) or SKINNY_RESIDUAL (out is float32 and the product is added into it).  Runs as an operation
     of the chain kernel (``csrc/gemm_chain.cu``): at once and alone, or, between ``chain_begin``
     and ``chain_end``, together with the products around it."""
     m, k = x.shape
@@ -433,12 +434,12 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
 
 
 def _skinny_out(out: torch.Tensor, m: int, n: int, epilogue: int, what: str) -> None:
-    cols = n // 2 if epilogue == SKINNY_SWIGLU else n
+    cols = n // 2 if epilogue in (SKINNY_SWIGLU, SKINNY_GLU) else n
     want = torch.float32 if epilogue in (SKINNY_F32, SKINNY_RESIDUAL) else torch.bfloat16
     if out.shape != (m, cols) or out.dtype != want or out.stride(1) != 1:
         raise KernelError(f"{what}: output must be [{m}, {cols}] {want}")
-    if epilogue == SKINNY_SWIGLU and n % 16:
-        raise KernelError(f"{what}: the SwiGLU epilogue needs groups of 8 gate and 8 up rows, got {n} rows")
+    if epilogue in (SKINNY_SWIGLU, SKINNY_GLU) and n % 16:
+        raise KernelError(f"{what}: a gated epilogue needs groups of 8 gate and 8 up rows, got {n} rows")
 
 
 def gemm_skinny_norm_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -666,13 +667,14 @@ def add_norm_groups(x: torch.Tensor, delta: Optional[torch.Tensor], delta_weight
         _ptr(out), _ptr(rows), n_out, hidden, _stream()), "add_norm_groups")
 
 
-def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, paired: bool = False) -> None:
     """out = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit);
-    ``gate_up`` rows hold the gate features, then the up features."""
+    ``gate_up`` rows hold the gate features, then the up features, or with ``paired`` groups of 8 gate
+    features followed by their 8 up features."""
     n, inter = out.shape
     _dev(gate_up, out.dtype, "glu_clamped input")
-    _check(_typed("q25_glu_clamped", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, float(limit), float(alpha), _stream()),
-           "glu_clamped")
+    _check(_typed("q25_glu_clamped", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, float(limit), float(alpha), int(paired),
+                                                _stream()), "glu_clamped")
 
 
 # ---- the gated linear recurrence -------------------------------------------------------------------

@@ -170,7 +170,9 @@ class RoutedGLU(FeedForward):
 class ClampedGLU(FeedForward):
     """A dense gated feed-forward with clamped branches, no biases: ``g = min(Wg h, limit)``,
     ``u = clamp(Wu h, -limit, limit)``, ``Wd (g * sigmoid(alpha g) * (u + 1))``: the form of one expert of
-    ``routed_glu``, used by every token.  gate and up are one product."""
+    ``routed_glu``, used by every token.  gate and up are one product, and in bfloat16 the unit is that
+    product's epilogue: in the weight-streaming kernel for steps of up to 8 rows, in the tcgen05 product for
+    long steps; between the two a kernel of its own follows the library's product."""
 
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
     accepts_residual = True          # the down projection can add into the residual stream itself
@@ -185,11 +187,26 @@ class ClampedGLU(FeedForward):
         return (TensorSpec("gate", (i, h)), TensorSpec("up", (i, h)), TensorSpec("down", (h, i)))
 
     def load(self, tensors, device, dtype):
-        gu = torch.cat([tensors["gate"], tensors["up"]], dim=0)
-        self.gate_up_proj = Linear(gu.to(device=device, dtype=dtype).contiguous())
+        gate, up = tensors["gate"].to(device), tensors["up"].to(device)
+        # bfloat16: rows in groups of 16 (8 gate features, then their 8 up features), so that the products' kernels
+        # can form the unit in their epilogue, as for ``swiglu``
+        self.paired = dtype == torch.bfloat16 and self.intermediate_size % 8 == 0
+        if self.paired:
+            h = self.hidden_size
+            gu = torch.stack([gate.reshape(-1, 8, h), up.reshape(-1, 8, h)], dim=1).reshape(2 * self.intermediate_size, h)
+        else:
+            gu = torch.cat([gate, up], dim=0)
+        self.gate_up_proj = Linear(gu.to(dtype=dtype).contiguous())
         self.down_proj = Linear(tensors["down"].to(device=device, dtype=dtype).contiguous())
+        self.constants = torch.tensor([self.limit, self.alpha], dtype=torch.float32, device=device)     # what the fused epilogue reads
 
     def forward(self, ctx, h, residual=None):
         act = torch.empty((h.shape[0], self.intermediate_size), dtype=ctx.dtype, device=h.device)
-        kernels.glu_clamped(self.gate_up_proj(h), act, self.limit, self.alpha)
+        w = self.gate_up_proj.weight
+        if self.paired and kernels.gemm_skinny_supports(h, w):
+            kernels.gemm_skinny(h, w, self.constants, act, kernels.SKINNY_GLU)
+        elif self.paired and linear.use_tcgen05(h, w, fused_epilogue=True):
+            kernels.gemm_tcgen05(h, w, self.constants, act, kernels.SKINNY_GLU)
+        else:
+            kernels.glu_clamped(self.gate_up_proj(h), act, self.limit, self.alpha, self.paired)
         return self.down_proj(act, residual=residual)

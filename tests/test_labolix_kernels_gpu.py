@@ -269,3 +269,31 @@ def test_retention_in_portions_with_state(dtype, heads, dim, vdim, dims):
     for k in lens:
         err = np.abs(torch.cat(got[k]).double().cpu().numpy() - want[k]).max()
         assert err < (2e-4 if dtype == torch.float32 else 6e-2), (k, err)
+
+
+# ---- the dense clamped gated feed-forward -----------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [3, 8, 40, 300])
+@pytest.mark.parametrize("hidden,inter", [(128, 96), (256, 200), (96, 44)])
+def test_clamped_glu_feed_forward(dtype, rows, hidden, inter):
+    """Steps of up to 8 rows (the unit in the weight-streaming product's epilogue), of some dozens (a kernel of
+    its own behind the library's product, on the paired layout) and of hundreds (the tcgen05 product's epilogue);
+    a width that has no paired layout (44) takes the plain layout everywhere."""
+    from qwen25vl_lite.parts.feed_forward import ClampedGLU
+
+    g = torch.Generator(device=DEV).manual_seed(5)
+    rnd = lambda *shape, scale=1.0: torch.randn(*shape, generator=g, device=DEV) * scale
+    tensors = {"gate": rnd(inter, hidden, scale=0.2), "up": rnd(inter, hidden, scale=0.2), "down": rnd(hidden, inter, scale=0.2)}
+    tensors = {k: v.to(dtype).float() for k, v in tensors.items()}       # what bfloat16 can hold, in both runs
+    part = ClampedGLU(hidden, inter, 1.25, 1.702)
+    part.load(tensors, DEV, dtype)
+    h = rnd(rows, hidden).to(dtype)
+    out = part.forward(SimpleNamespace(dtype=dtype), h)
+    x, w = h.double(), {k: v.double() for k, v in tensors.items()}
+    gate, up = (x @ w["gate"].T).clamp(max=1.25), (x @ w["up"].T).clamp(-1.25, 1.25)
+    want = (gate * torch.sigmoid(1.702 * gate) * (up + 1)) @ w["down"].T
+    assert (gate == 1.25).any() and (up == -1.25).any()                 # the clamps were reached
+    err = (out.double() - want).abs().max()
+    assert err < (2e-5 if dtype == torch.float32 else 0.03 * float(want.abs().max())), float(err)
