@@ -12,14 +12,14 @@
 // and the write of a step's keys and values into their pages, where the values may first be mixed
 // with those another layer computed for the same token: v <- (1 - mix) v + mix v_other.
 //
-// This file holds the general kernels (float or bfloat16, any sizes up to 256): one warp per
+// This file holds the general kernels (float or bfloat16, keys of any size, values of up to 512 channels): one warp per
 // (token, query head); keys are walked in tiles of 32 aligned to the absolute key index, first the
 // kept tokens that the window has left behind, then the window; scores, bias and softmax in float.
 // The order of every sum depends on the query's position alone.
 #include "common.cuh"
 
 #define BATT_WARPS 4
-#define BATT_MAX_D 256
+#define BATT_MAX_D 512
 
 template <typename T>
 __global__ void biased_attention_generic_kernel(

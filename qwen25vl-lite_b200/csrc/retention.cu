@@ -30,7 +30,8 @@ struct RetentionArgs {
   int heads, D, Dv, P;
   float k_scale, eps;
   // chunked runs
-  const int* chunks;      // (entry, first token of the chunk within the entry) pairs
+  int s_global;           // the walk with S in shared memory leaves S in global memory instead: heads too large for it
+  const int* chunks;      // (entry, first token row, tokens, last of its run) per chunk
   float* sums;            // [chunks, heads, D, Dv]: a chunk's own sum, then the S before the chunk
 };
 
@@ -71,8 +72,7 @@ __global__ void retention_scan_kernel(RetentionArgs a, int long_from) {
   pdl_wait();
   extern __shared__ __align__(16) float ret_smem[];
   const int D = a.D, Dv = a.Dv, P = a.P;
-  float* S = ret_smem;                 // [D][Dv]
-  float* q = S + (size_t)D * Dv;       // [D]
+  float* q = ret_smem + (a.s_global ? 0 : (size_t)D * Dv);       // [D]
   float* k = q + D;                    // [D]
   float* part = k + D;                 // [P][Dv]
   float* scratch = part + P * Dv;      // [32]
@@ -96,7 +96,10 @@ __global__ void retention_scan_kernel(RetentionArgs a, int long_from) {
   float* Sreq = a.state + ((size_t)a.slot_ids[entry] * a.heads + head) * SZ;
   float* Ssum = MODE == 0 ? nullptr : a.sums + ((size_t)blockIdx.x * a.heads + head) * SZ;
   const float* Sin = MODE == 0 ? Sreq : Ssum;
-  for (int x = threadIdx.x; x < D * Dv; x += blockDim.x) S[x] = MODE == 1 ? 0.f : Sin[x];
+  // [D][Dv]: in shared memory, or where it lies in global memory (an element is only ever touched by its owner thread)
+  float* S = a.s_global ? (MODE == 0 ? Sreq : Ssum) : ret_smem;
+  if (!a.s_global || MODE == 1)
+    for (int x = threadIdx.x; x < D * Dv; x += blockDim.x) S[x] = MODE == 1 ? 0.f : Sin[x];
   const bool active = threadIdx.x < Dv * P;       // the CTA is filled up to whole warps; the extra threads only copy
   const int j = threadIdx.x % Dv, p = active ? (int)threadIdx.x / Dv : -1;
   const int rows = D / P, i0 = p * rows;
@@ -124,7 +127,7 @@ __global__ void retention_scan_kernel(RetentionArgs a, int long_from) {
   }
   __syncthreads();
   float* Sout = MODE == 1 ? Ssum : (is_last ? Sreq : nullptr);
-  if (Sout)
+  if (Sout && Sout != S)
     for (int x = threadIdx.x; x < D * Dv; x += blockDim.x) Sout[x] = S[x];
 }
 
@@ -348,7 +351,7 @@ static int retention_run(const void* x, int x_row, int q_off, int k_off, int v_o
   a.x = x; a.x_row = x_row; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.g_off = g_off;
   a.angles = angles; a.half = half; a.layout = layout; a.decay = decay; a.state = state; a.cu_q = cu_q; a.slot_ids = slot_ids;
   a.out = out; a.heads = heads; a.D = D; a.Dv = Dv; a.P = retention_parts(D, Dv); a.k_scale = k_scale; a.eps = eps;
-  a.chunks = chunks; a.sums = sums;
+  a.chunks = chunks; a.sums = sums; a.s_global = 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int per = (int)(((size_t)D * Dv + 255) / 256);
   const dim3 fold_grid(n_runs > 0 ? n_runs : 1, heads, per < 64 ? per : 64);
@@ -380,7 +383,11 @@ static int retention_run(const void* x, int x_row, int q_off, int k_off, int v_o
     }
   }
   // any other sizes: S in shared memory
-  const size_t smem = ((size_t)D * Dv + 2 * D + (size_t)a.P * Dv + 32) * sizeof(float);
+  size_t smem = ((size_t)D * Dv + 2 * D + (size_t)a.P * Dv + 32) * sizeof(float);
+  if (smem > 200 * 1024) {                       // a head whose S does not fit: it stays in global memory, walked in place
+    a.s_global = 1;
+    smem = ((size_t)2 * D + (size_t)a.P * Dv + 32) * sizeof(float);
+  }
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(retention_scan_kernel<T, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -751,8 +751,8 @@ def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torc
     inside the key rows (0: the values have pages of their own, rows of ``dv`` channels)."""
     if sink is not None:
         _dev(sink, torch.float32, "attention sink")
-    if dv > 256:
-        raise KernelError(f"attention: value size {dv} is beyond 256")
+    if dv > 512:
+        raise KernelError(f"attention: value size {dv} is beyond 512")
     _check(_typed("q25_biased_attention_generic", qkv.dtype)(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), cu_q.data_ptr(), q_start_pos.data_ptr(), qkv.shape[0], nq, nkv, dk, dv,

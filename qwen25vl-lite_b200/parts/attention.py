@@ -199,8 +199,8 @@ class SinkAttention(Mixer):
             raise ValueError(f"sink is None, 'zero' or 'learned', got {sink!r}")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.value_dim = self.head_dim if value_dim is None else int(value_dim)
-        if not 0 < self.value_dim <= 256 or self.head_dim <= 0:
-            raise ValueError(f"key size {head_dim} / value size {value_dim} is not supported: values take up to 256 channels")
+        if not 0 < self.value_dim <= 512 or self.head_dim <= 0:
+            raise ValueError(f"key size {head_dim} / value size {value_dim} is not supported: values take up to 512 channels")
         self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)
         self.window = None if not window else int(window)
         self.sink_kind, self.position = sink, position
@@ -270,8 +270,8 @@ class LatentAttention(Mixer):
             raise ValueError(f"sink is None, 'zero' or 'learned', got {sink!r}")
         self.hidden_size, self.num_heads, self.head_dim, self.rot_dim = int(hidden_size), int(num_heads), int(head_dim), int(rot_dim)
         self.value_dim, self.kv_rank = int(value_dim), int(kv_rank)
-        if not 0 < self.kv_rank <= 256:
-            raise ValueError(f"the latent takes up to 256 channels, got {kv_rank}")
+        if not 0 < self.kv_rank <= 512:
+            raise ValueError(f"the latent takes up to 512 channels, got {kv_rank}")
         self.scale, self.norm_eps = float(scale), float(norm_eps)
         self.window = None if not window else int(window)
         self.sink_kind, self.position = sink, position

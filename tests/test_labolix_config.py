@@ -12,7 +12,7 @@ from qwen25vl_lite.config import ConfigError, resolve_architecture
 from qwen25vl_lite.config.labolix_config import LabolixConfig
 from qwen25vl_lite.models.decoder import DecoderModel
 from qwen25vl_lite.parts.position import rotary_frequencies
-from tiny_labolix import L1, L2, L3, L4, TINY, make_model_dir
+from tiny_labolix import L1, L2, L3, L4, L5, TINY, make_model_dir
 
 
 def model_of(raw):
@@ -140,4 +140,4 @@ def test_known_architectures_include_the_design():
     from qwen25vl_lite.config import known_architectures
 
     assert {"Labolix", "Rirulix"} <= set(known_architectures())
-    assert [L1, L2, L3, L4][0]["architecture"] == "Labolix"
+    assert all(c["architecture"] == "Labolix" for c in (L1, L2, L3, L4, L5))

@@ -229,7 +229,8 @@ def retention_reference(x, heads, dim, vdim, decay, freqs, positions, eps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dim,vdim,dims", [(3, 16, 24, 8), (2, 64, 32, 64), (5, 12, 20, 12), (2, 128, 128, 0), (1, 40, 8, 20)])
+@pytest.mark.parametrize("heads,dim,vdim,dims", [(3, 16, 24, 8), (2, 64, 32, 64), (5, 12, 20, 12), (2, 128, 128, 0), (1, 40, 8, 20), (2, 10, 14, 4),
+                                                  (1, 256, 256, 64)])
 def test_retention_in_portions_with_state(dtype, heads, dim, vdim, dims):
     """Two requests of unequal length in four steps (portions of 1, 2 and many tokens, the second request
     absent from a step), in slots 2 and 0 of three; then a third request in the slot the second one

@@ -1,7 +1,7 @@
 """Tiny configurations of the Labolix design for the tests, and the helper that writes them as model
 folders with random weights.
 
-The four differ in every size and option: widths, vocabularies, layer orders, which layers run with
+The five differ in every size and option: widths, vocabularies, layer orders, which layers run with
 another layer's tensors (none, one, several, of every mixer), head counts and groupings (grouped, one
 kv head, as many kv heads as query heads), key and value sizes (equal and not), how many channels of
 a head are turned (all, some, none), scaled frequencies or plain ones, windows (shorter than a page,
@@ -93,7 +93,19 @@ L4 = _config(120, 80, 1e-6, 8.0, [
     {"type": "retention", "mixer": _ret(2, 40, 8, [0.96875, 0.6], _rot(20, 77.0)), "mlp": _mlp(20, 1.5)},
 ])
 
-TINY = {"L1": (L1, 21, 16), "L2": (L2, 22, 8), "L3": (L3, 23, 16), "L4": (L4, 24, 16)}      # config, weight seed, page size
+# 4 layers of awkward sizes, none a multiple of 8: width 100, vocabulary 77; attention of 3 heads on one kv head,
+# keys of 24 with 6 turned channels, values of 20; latent attention of 5 heads of 12 + 6 over rank 18, values of 10, a
+# window of 7 (less than half a page) and plain frequencies; retention of 3 heads of 10 x 14 with 4 turned channels; a
+# feed-forward of 50; the attention layer once more.  Every kernel takes its general path here.
+_L5_ATT = {"type": "attention", "mixer": _attn(3, 1, 24, 20, 0.21, _rot(6, 300.0, WAVE)), "mlp": _mlp(50, 1.25)}
+L5 = _config(77, 100, 1e-5, 9.0, [
+    _L5_ATT,
+    {"type": "latent_attention", "mixer": _latent(5, 12, 6, 10, 18, 0.24, 7, _rot(6, 2000.0)), "mlp": _mlp(50, 1.25)},
+    {"type": "retention", "mixer": _ret(3, 10, 14, [0.9, 0.96875, 0.75], _rot(4, 50.0)), "mlp": _mlp(30, 2.0)},
+    dict(_L5_ATT, weights_of=0),
+])
+
+TINY = {"L1": (L1, 21, 16), "L2": (L2, 22, 8), "L3": (L3, 23, 16), "L4": (L4, 24, 16), "L5": (L5, 25, 16)}      # config, weight seed, page size
 
 GAIN = 10.0         # what the matrices of the layers are multiplied by
 SINK_GAIN = 60.0    # ... the learned sinks
