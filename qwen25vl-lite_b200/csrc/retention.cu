@@ -275,13 +275,15 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_rows_kernel(Retenti
         for (int t = b * RET_TB; t < t_end; ++t) {
           const int slot = (b & 1) * RET_TB + (t - b * RET_TB);
           const float vj = vs[slot * Dv + j];
-          const float2* row = kq + slot * D + i0;
+          const float4* row = reinterpret_cast<const float4*>(kq + slot * D + i0);       // two rows a load
           float acc = 0.f;
 #pragma unroll
-          for (int r = 0; r < ROWS; ++r) {
-            const float2 x = row[r];
+          for (int r = 0; r < ROWS; r += 2) {
+            const float4 x = row[r >> 1];
             s[r] = fmaf(decay, s[r], x.x * vj);
             acc = fmaf(s[r], x.y, acc);
+            s[r + 1] = fmaf(decay, s[r + 1], x.z * vj);
+            acc = fmaf(s[r + 1], x.w, acc);
           }
           if (mode != 1) obuf[((size_t)p * group + t) * Dv + j] = acc;
         }
