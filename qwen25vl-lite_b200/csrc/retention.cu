@@ -169,7 +169,8 @@ __global__ void retention_fold_kernel(RetentionArgs a, const int* __restrict__ r
 // keys and queries of the next RET_TB tokens into one half of a double buffer (with the values) while
 // the others work through the half before, so that no trip to memory stands in the walk; the CTA meets
 // once per RET_TB tokens.  The raw outputs of up to `group` tokens wait in shared memory, each part's
-// share apart, and are normalised and gated afterwards, a warp per token.  mode as MODE above.
+// share apart, beside the tokens' gates (the loaders bring them with the values), and are normalised and
+// gated afterwards, a warp per token, with no trip to memory but the store.  mode as MODE above.
 #define RET_TB 4
 #define RET_LOADERS 128
 #define RET_MAX_THREADS 640   // 512 that compute and the loaders: registers for 32 rows of S a thread
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_rows_kernel(Retenti
   float2* kq = reinterpret_cast<float2*>(ret_smem);   // [2][RET_TB][D]: (scaled rotated key, rotated query)
   float* vs = ret_smem + 2 * 2 * RET_TB * D;          // [2][RET_TB][Dv]
   float* obuf = vs + 2 * RET_TB * Dv;                 // [P][group][Dv]
+  float* gs = obuf + (size_t)P * group * Dv;          // [group][Dv]: the tokens' gates, brought by the loaders with the values
   const int head = blockIdx.y;
   int entry, first, last;
   bool is_last = true;
@@ -235,13 +237,14 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_rows_kernel(Retenti
         const int cv = is_v ? c : 0, ck_u = is_k ? iu : 0, ck_v = is_k ? iv : 0, ia = turn ? i : 0;
         const T* row0 = X + (size_t)t0 * a.x_row;
         const float* ang0 = a.angles ? a.angles + ((size_t)t0 * half + ia) * 2 : nullptr;
-        T raw[RET_TB], ku[RET_TB], kv[RET_TB], qu[RET_TB], qv[RET_TB];
+        T raw[RET_TB], gat[RET_TB], ku[RET_TB], kv[RET_TB], qu[RET_TB], qv[RET_TB];
         float2 cssn[RET_TB];
 #pragma unroll
         for (int tt = 0; tt < RET_TB; ++tt) {
           const int tc = tt < nt ? tt : nt - 1;
           const T* row = row0 + (size_t)tc * a.x_row;
           raw[tt] = row[a.v_off + (size_t)head * Dv + cv];
+          gat[tt] = row[a.g_off + (size_t)head * Dv + cv];
           ku[tt] = row[a.k_off + (size_t)head * D + ck_u];
           kv[tt] = row[a.k_off + (size_t)head * D + ck_v];
           qu[tt] = row[a.q_off + (size_t)head * D + ck_u];
@@ -251,7 +254,10 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_rows_kernel(Retenti
 #pragma unroll
         for (int tt = 0; tt < RET_TB; ++tt) {
           if (tt < nt) {
-            if (is_v) vs[(base + tt) * Dv + c] = to_f32(raw[tt]);
+            if (is_v) {
+              vs[(base + tt) * Dv + c] = to_f32(raw[tt]);
+              if (mode != 1) gs[(size_t)(b * RET_TB + tt) * Dv + c] = to_f32(gat[tt]);
+            }
             if (is_k) {
               const float u = to_f32(ku[tt]), v = to_f32(kv[tt]), uq = to_f32(qu[tt]), vq = to_f32(qv[tt]);
               const float cs = cssn[tt].x, sn = cssn[tt].y;
@@ -294,10 +300,6 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_rows_kernel(Retenti
       const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
       for (int t = warp; t < cnt; t += nwarps) {
         const size_t tok = (size_t)(g0 + t);
-        const T* grow = X + tok * a.x_row + a.g_off + (size_t)head * Dv;
-        T gate[4];                                                       // the first 128 channels' gates, asked for ahead of the sums
-#pragma unroll
-        for (int u = 0; u < 4; ++u) gate[u] = grow[min(lane + 32 * u, Dv - 1)];
         float ss = 0.f;
         for (int jj = lane; jj < Dv; jj += 32) {
           float o = 0.f;
@@ -308,14 +310,8 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_rows_kernel(Retenti
         ss = warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
         T* orow = reinterpret_cast<T*>(a.out) + tok * a.heads * Dv + (size_t)head * Dv;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int jj = lane + 32 * u;
-          const float g = to_f32(gate[u]);
-          if (jj < Dv) orow[jj] = from_f32<T>(obuf[(size_t)t * Dv + jj] * inv * (g / (1.0f + expf(-g))));
-        }
-        for (int jj = lane + 128; jj < Dv; jj += 32) {
-          const float g = to_f32(grow[jj]);
+        for (int jj = lane; jj < Dv; jj += 32) {
+          const float g = gs[(size_t)t * Dv + jj];
           orow[jj] = from_f32<T>(obuf[(size_t)t * Dv + jj] * inv * (g / (1.0f + expf(-g))));
         }
       }
@@ -365,7 +361,7 @@ static int retention_run(const void* x, int x_row, int q_off, int k_off, int v_o
     const int P = D / rows, compute = (Dv * P + 31) / 32 * 32;
     int group = 16384 / (P * Dv);
     group = group > 64 ? 64 : (group < 1 ? 1 : group);
-    const size_t smem = ((size_t)2 * 2 * RET_TB * D + (size_t)2 * RET_TB * Dv + (size_t)P * group * Dv) * sizeof(float);
+    const size_t smem = ((size_t)2 * 2 * RET_TB * D + (size_t)2 * RET_TB * Dv + (size_t)(P + 1) * group * Dv) * sizeof(float);
     if (compute + RET_LOADERS <= RET_MAX_THREADS && smem <= 200 * 1024) {
       void (*kernel)(RetentionArgs, int, int, int) =
           rows == 32 ? retention_rows_kernel<T, 32> : rows == 16 ? retention_rows_kernel<T, 16>
